@@ -1,0 +1,104 @@
+// Shared device helpers of the sm_100a kernels: element conversion, reductions,
+// 16-byte vector access.  Every exported entry point is `extern "C"`, takes raw
+// device pointers plus the stream to launch on, allocates nothing, and returns
+// the cudaError_t of its launch as an int (0 = success).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+typedef __nv_bfloat16 bf16;
+
+#define Q3_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Error codes of argument checks, above the cudaError_t range.
+#define Q3_ERR_BAD_SIZE 10001
+#define Q3_ERR_TOO_LARGE 10002
+#define Q3_ERR_MISALIGNED 10003
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// Rounds a 32-bit value to the storage type and back: the identity for float,
+// one bfloat16 rounding for bf16.
+template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f32<T>(from_f32<T>(v)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; `scratch` holds 33 floats.  Every thread
+// gets the result.  The order of the additions is fixed by the thread layout.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < n_warps ? scratch[lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_warps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < n_warps ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// A 16-byte packet of elements of type T.
+template <typename T> struct Pack;
+template <> struct Pack<float> {
+    static constexpr int N = 4;
+    float4 raw;
+    __device__ __forceinline__ float get(int i) const { return (&raw.x)[i]; }
+    __device__ __forceinline__ void set(int i, float v) { (&raw.x)[i] = v; }
+};
+template <> struct Pack<bf16> {
+    static constexpr int N = 8;
+    uint4 raw;
+    __device__ __forceinline__ float get(int i) const {
+        return __bfloat162float(reinterpret_cast<const bf16*>(&raw)[i]);
+    }
+    __device__ __forceinline__ void set(int i, float v) { reinterpret_cast<bf16*>(&raw)[i] = __float2bfloat16_rn(v); }
+};
+
+template <typename T> __device__ __forceinline__ Pack<T> load_pack(const T* p) {
+    Pack<T> r;
+    r.raw = *reinterpret_cast<const decltype(r.raw)*>(p);
+    return r;
+}
+template <typename T> __device__ __forceinline__ void store_pack(T* p, const Pack<T>& v) {
+    *reinterpret_cast<decltype(v.raw)*>(p) = v.raw;
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -1,0 +1,198 @@
+"""Python face of the CUDA entry points: tensors in, launches on torch's current stream.
+
+Each function checks what the kernel relies on (device, dtype, contiguity, sizes),
+passes raw pointers to the `extern "C"` entry point and raises `KernelError` if the
+launch reports an error.  Nothing here computes on the host and nothing falls back
+to a library: a CPU tensor or a missing compiler is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_uint64, c_void_p
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+_ERRORS = {10001: "a size the kernel does not take", 10002: "more rows than one launch takes",
+           10003: "a pointer or stride that is not 16-byte aligned"}
+_SUFFIX = {torch.float32: "f32", torch.bfloat16: "bf16"}
+_fn_cache = {}
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or its launch failed."""
+
+
+def _fn(source: str, name: str, argtypes, defines=()):
+    key = (source, name, tuple(defines))
+    fn = _fn_cache.get(key)
+    if fn is None:
+        lib = load_library(source, defines)
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        _fn_cache[key] = fn
+    return fn
+
+
+def _check(code: int, name: str):
+    if code != 0:
+        what = _ERRORS.get(code)
+        if what is None:
+            what = f"CUDA error {code} at launch"
+        raise KernelError(f"{name}: {what}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev(t: torch.Tensor, name: str, dtype=None):
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    return t.data_ptr()
+
+
+def _suffix(t: torch.Tensor) -> str:
+    try:
+        return _SUFFIX[t.dtype]
+    except KeyError:
+        raise KernelError(f"element type {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _ptr(t: Optional[torch.Tensor], name: str, dtype=None):
+    return None if t is None else _dev(t, name, dtype)
+
+
+# ------------------------------------------------------------------ elementwise
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = table[ids[t]]; ids int32 [N], table [V, H], out [N, H]."""
+    s = _suffix(table)
+    fn = _fn("elementwise.cu", f"q3_embedding_{s}", [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p])
+    n = ids.numel()
+    if out.shape[0] < n or out.shape[1] != table.shape[1] or out.dtype != table.dtype:
+        raise KernelError("embedding: output does not fit")
+    _check(fn(_dev(ids, "ids", torch.int32), _dev(table, "table"), _dev(out, "out"), n, table.shape[1],
+              table.shape[0], _stream()), "embedding")
+    return out
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+             delta: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = RMSNorm(x) * weight over the last dimension; weight is float32.
+
+    With `delta`, first x += delta in place (32-bit sum, stored in x's type) and the
+    norm reads the stored sum.  x: [..., size] with contiguous rows."""
+    s = _suffix(x)
+    size = x.shape[-1]
+    rows = x.numel() // size if size else 0
+    if weight.numel() != size or out.shape != x.shape or out.dtype != x.dtype:
+        raise KernelError("rms_norm: weight or output does not fit")
+    if delta is not None and (delta.shape != x.shape or delta.dtype != x.dtype):
+        raise KernelError("rms_norm: delta does not fit")
+    fn = _fn("elementwise.cu", f"q3_rms_norm_{s}",
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_int64, c_int64, c_void_p])
+    _check(fn(_dev(x, "x"), _ptr(delta, "delta"), _dev(weight, "weight", torch.float32), _dev(out, "out"),
+              rows, size, float(eps), size, size, _stream()), "rms_norm")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r, c] = silu(gate_up[r, c]) * gate_up[r, inter + c]."""
+    s = _suffix(gate_up)
+    rows, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (rows, two_i // 2) or out.dtype != gate_up.dtype:
+        raise KernelError("silu_mul: output does not fit")
+    fn = _fn("elementwise.cu", f"q3_silu_mul_{s}", [c_void_p, c_void_p, c_int64, c_int, c_void_p])
+    _check(fn(_dev(gate_up, "gate_up"), _dev(out, "out"), rows, two_i // 2, _stream()), "silu_mul")
+    return out
+
+
+def gather_rows(x: torch.Tensor, idx: torch.Tensor, out: torch.Tensor, delta: Optional[torch.Tensor] = None):
+    """out[r] = x[idx[r]] (+ delta[idx[r]], summed in 32-bit)."""
+    s = _suffix(x)
+    rows, size = idx.numel(), x.shape[-1]
+    if out.shape[0] < rows or out.shape[-1] != size or out.dtype != x.dtype:
+        raise KernelError("gather_rows: output does not fit")
+    fn = _fn("elementwise.cu", f"q3_gather_rows_{s}", [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p])
+    _check(fn(_dev(x, "x"), _ptr(delta, "delta", x.dtype), _dev(idx, "idx", torch.int32), _dev(out, "out"),
+              rows, size, _stream()), "gather_rows")
+    return out
+
+
+# ------------------------------------------------------------------ matrix products
+def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T in true 32-bit (fmaf, fixed order over K)."""
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm_f32: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    fn = _fn("gemm_f32.cu", "q3_gemm_tn_f32",
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_void_p])
+    _check(fn(_dev(x, "x", torch.float32), _dev(w, "w", torch.float32), _dev(out, "out", torch.float32),
+              M, N, K, K, K, N, _stream()), "gemm_f32")
+    return out
+
+
+# ------------------------------------------------------------------ attention
+def qkv_prepare(qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, cos, sin, token_seq, token_pos, page_table,
+                n_tokens: int, nq: int, nkv: int, d: int, eps: float):
+    """Per-head norm of q and k, rotation, and the write of k and v into the cache pages."""
+    s = _suffix(qkv)
+    if d % 16 != 0 or d > 256:
+        raise KernelError(f"head_dim {d} is not supported: multiples of 16 up to 256")
+    if qkv.shape[-1] != (nq + 2 * nkv) * d or k_pages.dtype != qkv.dtype or k_pages.shape[1:] != (nkv, 64, d):
+        raise KernelError("qkv_prepare: shapes do not fit")
+    fn = _fn("attention.cu", f"q3_qkv_prepare_{s}",
+             [c_void_p] * 11 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_dev(qkv, "qkv"), _dev(q_out, "q_out", qkv.dtype), _dev(k_pages, "k_pages"), _dev(v_pages, "v_pages"),
+              _ptr(q_norm_w, "q_norm_w", torch.float32), _ptr(k_norm_w, "k_norm_w", torch.float32),
+              _ptr(cos, "cos", torch.float32), _ptr(sin, "sin", torch.float32),
+              _dev(token_seq, "token_seq", torch.int32), _dev(token_pos, "token_pos", torch.int32),
+              _dev(page_table, "page_table", torch.int32), page_table.shape[-1], n_tokens, nq, nkv, d, float(eps),
+              _stream()), "qkv_prepare")
+    return q_out
+
+
+def attention_generic(q, k_pages, v_pages, out, token_seq, token_pos, page_table, n_tokens: int, nq: int, nkv: int,
+                      d: int, scale: float, window: Optional[int] = None):
+    """Causal grouped-query attention of every token of the step over its sequence's pages."""
+    s = _suffix(q)
+    if d % 16 != 0 or d > 256:
+        raise KernelError(f"head_dim {d} is not supported: multiples of 16 up to 256")
+    fn = _fn("attention.cu", f"q3_attention_generic_{s}",
+             [c_void_p] * 7 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(fn(_dev(q, "q"), _dev(k_pages, "k_pages", q.dtype), _dev(v_pages, "v_pages", q.dtype),
+              _dev(out, "out", q.dtype), _dev(token_seq, "token_seq", torch.int32),
+              _dev(token_pos, "token_pos", torch.int32), _dev(page_table, "page_table", torch.int32),
+              page_table.shape[-1], n_tokens, nq, nkv, d, float(scale), int(window or 0), _stream()),
+           "attention_generic")
+    return out
+
+
+# ------------------------------------------------------------------ sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor, valid: Optional[int] = None) -> torch.Tensor:
+    """out[r] = index of the highest logit of row r (lowest id among equals, NaN as -inf)."""
+    rows, vocab = logits.shape
+    fn = _fn("sampling.cu", "q3_argmax_f32", [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_dev(logits, "logits", torch.float32), vocab, rows, int(valid or vocab),
+              _dev(out, "out", torch.int32), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int,
+           seq_ids: torch.Tensor, steps: torch.Tensor, valid: Optional[int] = None) -> torch.Tensor:
+    """One draw per row; out[r] = -1 marks a row with a non-finite logit."""
+    rows, vocab = logits.shape
+    fn = _fn("sampling.cu", "q3_sample_f32",
+             [c_void_p, c_int64, c_int, c_int, c_float, c_int, c_float, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_dev(logits, "logits", torch.float32), vocab, rows, int(valid or vocab), float(temperature), int(top_k),
+              float(top_p), int(seed) & 0xFFFFFFFFFFFFFFFF, _dev(seq_ids, "seq_ids", torch.int64),
+              _dev(steps, "steps", torch.int32), _dev(out, "out", torch.int32), _stream()), "sample")
+    return out

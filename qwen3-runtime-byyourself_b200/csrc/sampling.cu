@@ -1,0 +1,256 @@
+// Token choice on the GPU: greedy argmax, and temperature / top-k / top-p sampling.
+//
+// The reference chooses greedily on the GPU (src/ops/argmax.cu:34-100: lowest id among
+// equals, NaN counts as -inf, optional valid prefix) but samples on the CPU after
+// copying the logits to the host (src/generation/sampler.cpp:137-247).  Here both stay
+// on the device, one block per row, and only the chosen ids leave it.
+//
+// Sampling keeps the reference's order and meaning: score = logit / temperature; top-k
+// keeps every candidate whose score reaches the k-th best (ties beyond k stay);
+// candidates are ordered by score, lower id first among equals; weight = exp(score -
+// max); top-p keeps the shortest prefix whose weight reaches top_p of the total; the
+// draw takes r = u * kept weight and the first candidate whose cumulative weight
+// exceeds r.  Instead of sorting, the kernel finds each boundary by radix selection
+// over the order-preserving bit pattern of the logits: equal logits have equal
+// weights, so a boundary inside a run of equals is plain arithmetic.  Weights are
+// summed as 64-bit fixed point (2^-40 units), which makes the sums independent of the
+// order of the additions; a weight below 2^-41 counts as zero.
+//
+// The uniform number is not the reference's shared mt19937_64 stream (which makes a
+// sequence's tokens depend on what else is in the batch): it is a hash of (seed,
+// sequence id, step), so every sequence has a stream of its own.
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 512;
+constexpr double FIX_ONE = 1099511627776.0;  // 2^40
+
+__device__ __forceinline__ uint32_t float_key(float x) {
+    if (x == 0.0f) x = 0.0f;  // -0 and +0 are equal scores
+    const uint32_t b = __float_as_uint(x);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__device__ __forceinline__ float key_float(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
+}
+
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+__device__ __forceinline__ uint64_t fixed_weight(float logit, double temperature, double max_score) {
+    const double w = exp((double)logit / temperature - max_score);
+    return (uint64_t)(w * FIX_ONE + 0.5);
+}
+
+__global__ void __launch_bounds__(THREADS)
+argmax_kernel(const float* __restrict__ logits, int64_t stride, int valid, int* __restrict__ out) {
+    __shared__ float best_v[THREADS / 32];
+    __shared__ int best_i[THREADS / 32];
+    const float* x = logits + (int64_t)blockIdx.x * stride;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < valid; i += THREADS) {
+        float v = x[i];
+        if (isnan(v)) v = -INFINITY;
+        if (v > bv || bi == 0x7fffffff) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { best_v[threadIdx.x >> 5] = bv; best_i[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < THREADS / 32; ++w)
+            if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) { bv = best_v[w]; bi = best_i[w]; }
+        out[blockIdx.x] = bi;
+    }
+}
+
+struct Selected {
+    uint32_t key;      // bit pattern of the boundary logit
+    uint64_t before;   // weight (or count) of everything ordered before the run of `key`
+    uint64_t inside;   // weight (or count) of the run of `key`
+};
+
+// Finds the key at which the cumulative sum, taken from the highest key downwards,
+// first reaches `threshold` (1 <= threshold <= sum over all candidates).  WEIGHTED:
+// sums fixed-point weights of the candidates (key >= floor_key); otherwise counts all.
+template <bool WEIGHTED>
+__device__ Selected radix_select(const float* __restrict__ x, int valid, uint64_t threshold, uint32_t floor_key,
+                                 double temperature, double max_score, unsigned long long* hist, uint64_t* bcast) {
+    uint32_t prefix = 0, mask = 0;
+    uint64_t before = 0, inside = 0;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int b = threadIdx.x; b < 256; b += THREADS) hist[b] = 0ull;
+        __syncthreads();
+        for (int i = threadIdx.x; i < valid; i += THREADS) {
+            const float v = x[i];
+            const uint32_t key = float_key(v);
+            if ((key & mask) != prefix || key < floor_key) continue;
+            const unsigned long long add = WEIGHTED ? fixed_weight(v, temperature, max_score) : 1ull;
+            if (add) atomicAdd(&hist[(key >> shift) & 255u], add);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int chosen = -1, last_nonzero = 0;
+            uint64_t run = before;
+            for (int b = 255; b >= 0; --b) {
+                const uint64_t h = hist[b];
+                if (h == 0) continue;
+                last_nonzero = b;
+                if (run + h >= threshold) { chosen = b; break; }
+                run += h;
+            }
+            if (chosen < 0) {  // threshold above the total: settle on the last run
+                chosen = last_nonzero;
+                run -= hist[chosen];
+            }
+            bcast[0] = (uint64_t)chosen;
+            bcast[1] = run;
+            bcast[2] = hist[chosen];
+        }
+        __syncthreads();
+        prefix |= (uint32_t)bcast[0] << shift;
+        mask |= 255u << shift;
+        before = bcast[1];
+        inside = bcast[2];
+        __syncthreads();
+    }
+    return Selected{prefix, before, inside};
+}
+
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const float* __restrict__ logits, int64_t stride, int valid, float temperature_f, int top_k, float top_p,
+              uint64_t seed, const int64_t* __restrict__ seq_ids, const int* __restrict__ steps,
+              int* __restrict__ out) {
+    __shared__ unsigned long long hist[256];
+    __shared__ uint64_t bcast[3];
+    __shared__ float red[33];
+    __shared__ unsigned long long total_s;
+    __shared__ int counts[THREADS];
+    __shared__ int found[2];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float* x = logits + (int64_t)row * stride;
+
+    // the maximum, and a refusal of rows with NaN or Inf (the reference throws there)
+    float mx = -INFINITY;
+    int bad = 0;
+    for (int i = tid; i < valid; i += THREADS) {
+        const float v = x[i];
+        if (!isfinite(v)) bad = 1;
+        mx = fmaxf(mx, v);
+    }
+    bad = __syncthreads_or(bad);
+    if (bad) {
+        if (tid == 0) out[row] = -1;
+        return;
+    }
+    mx = block_max(mx, red);
+    const double temperature = (double)temperature_f;
+    const double max_score = (double)mx / temperature;
+
+    // top-k: the k-th best key; every key that reaches it stays
+    uint32_t floor_key = 0;
+    if (top_k > 0 && top_k < valid) {
+        floor_key = radix_select<false>(x, valid, (uint64_t)top_k, 0u, temperature, max_score, hist, bcast).key;
+    }
+
+    // total weight of the candidates
+    if (tid == 0) total_s = 0ull;
+    __syncthreads();
+    unsigned long long part = 0ull;
+    for (int i = tid; i < valid; i += THREADS) {
+        const float v = x[i];
+        if (float_key(v) >= floor_key) part += fixed_weight(v, temperature, max_score);
+    }
+    if (part) atomicAdd(&total_s, part);
+    __syncthreads();
+    const uint64_t total = total_s;  // >= 2^40: the maximum itself has weight one
+
+    // top-p: shortest prefix whose weight reaches top_p * total
+    uint64_t cut = (uint64_t)ceil((double)top_p * (double)total);
+    cut = cut < 1 ? 1 : (cut > total ? total : cut);
+    const Selected edge = radix_select<true>(x, valid, cut, floor_key, temperature, max_score, hist, bcast);
+    const uint64_t edge_w = fixed_weight(key_float(edge.key), temperature, max_score);
+    uint64_t edge_n = edge_w ? (cut - edge.before + edge_w - 1) / edge_w : 1;
+    const uint64_t edge_count = edge_w ? edge.inside / edge_w : 1;
+    edge_n = edge_n < 1 ? 1 : (edge_n > edge_count ? edge_count : edge_n);
+    const uint64_t kept = edge.before + edge_n * edge_w;
+
+    // the draw: first candidate whose cumulative weight exceeds r = u * kept
+    const uint64_t h = splitmix64(splitmix64(seed ^ splitmix64((uint64_t)seq_ids[row])) + (uint64_t)steps[row]);
+    const double u = (double)(h >> 11) * (1.0 / 9007199254740992.0);
+    uint64_t r = (uint64_t)(u * (double)kept);
+    if (r >= kept) r = kept - 1;
+    const Selected hit = radix_select<true>(x, valid, r + 1, floor_key, temperature, max_score, hist, bcast);
+    const uint64_t hit_w = fixed_weight(key_float(hit.key), temperature, max_score);
+    const uint64_t hit_count = hit_w ? hit.inside / hit_w : 1;
+    uint64_t nth = hit_w ? (r - hit.before) / hit_w : 0;  // 0-based place inside the run of equals
+    if (nth >= hit_count) nth = hit_count - 1;
+
+    // the nth lowest id among the logits equal to hit.key: contiguous id ranges per thread
+    const int chunk = (valid + THREADS - 1) / THREADS;
+    const int lo = tid * chunk, hi = min(valid, lo + chunk);
+    int mine = 0;
+    for (int i = lo; i < hi; ++i) mine += float_key(x[i]) == hit.key;
+    counts[tid] = mine;
+    __syncthreads();
+    if (tid == 0) {
+        int64_t left = (int64_t)nth;
+        int owner = -1, last_owner = -1;
+        for (int t = 0; t < THREADS; ++t) {
+            if (counts[t] == 0) continue;
+            last_owner = t;
+            if (left < counts[t]) { owner = t; break; }
+            left -= counts[t];
+        }
+        if (owner < 0) { owner = last_owner; left = last_owner >= 0 ? counts[last_owner] - 1 : 0; }
+        found[0] = owner;
+        found[1] = (int)left;
+    }
+    __syncthreads();
+    if (found[0] < 0) {
+        if (tid == 0) out[row] = -1;
+        return;
+    }
+    if (tid == found[0]) {
+        int left = found[1], id = -1;
+        for (int i = lo; i < hi; ++i) {
+            if (float_key(x[i]) == hit.key) {
+                if (left == 0) { id = i; break; }
+                --left;
+            }
+        }
+        out[row] = id;
+    }
+}
+
+}  // namespace
+
+Q3_EXPORT int q3_argmax_f32(const float* logits, int64_t stride, int rows, int valid, int* out, void* stream) {
+    if (rows <= 0) return 0;
+    if (valid <= 0 || valid > stride) return Q3_ERR_BAD_SIZE;
+    argmax_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(logits, stride, valid, out);
+    return (int)cudaGetLastError();
+}
+
+// out[row] = -1 marks a row with a non-finite logit.
+Q3_EXPORT int q3_sample_f32(const float* logits, int64_t stride, int rows, int valid, float temperature, int top_k,
+                            float top_p, uint64_t seed, const int64_t* seq_ids, const int* steps, int* out,
+                            void* stream) {
+    if (rows <= 0) return 0;
+    if (valid <= 0 || valid > stride || !(temperature > 0.0f) || top_k < 0 || !(top_p > 0.0f && top_p <= 1.0f))
+        return Q3_ERR_BAD_SIZE;
+    sample_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(logits, stride, valid, temperature, top_k, top_p, seed,
+                                                               seq_ids, steps, out);
+    return (int)cudaGetLastError();
+}

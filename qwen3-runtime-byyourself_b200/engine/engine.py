@@ -1,0 +1,200 @@
+"""The engine: a bound model, its cache, and the ONE step function.
+
+`Engine.step(entries)` runs exactly the tokens it is given - the prompts of a batch
+that starts together, or one token for each of its sequences - as one packed batch
+from the cache that earlier steps left, and returns float32 logits for the wanted
+positions.  Generation, trace replay, the benchmark and the tests all call it.
+
+The reference's counterpart is `qwen3_model_forward(token_ids[B,S], ..., start_position)`
+plus `qwen3_lm_head` (src/model/model.cpp:107-147, src/model/lm_head.cpp:183-192): a
+rectangular batch with one shared start position.  Its validations are kept per
+sequence: token ids inside the vocabulary (src/generation/generator.cpp:209-215),
+cache capacity (src/model/self_attention.cpp:91-100), positions inside the rotary
+table (src/model/model.cpp:81-88).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.storage import KVCache
+from ..config.registry import load_config
+from ..csrc.build import KernelBuildError
+from ..parts.model import Model, build_model
+from ..weights.loader import load_weights, random_weights
+from .context import Scratch, StepContext
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+          torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+@dataclass
+class StepEntry:
+    """One sequence's share of a step: its slot, its next tokens, and the places among
+    these tokens whose logits are wanted."""
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepError(ValueError):
+    """A step that cannot run: empty, out-of-vocabulary ids, a wanted place outside the tokens."""
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class _MetaLayout:
+    """Offsets of the sections of the step's int32 metadata buffer."""
+
+    def __init__(self, n_tokens: int, n_seqs: int, n_want: int, n_groups: int, pages_per_slot: int):
+        o = 0
+        self.token_ids = o; o += _align4(n_tokens)
+        self.token_seq = o; o += _align4(n_tokens)
+        self.token_pos = o; o += _align4(n_tokens)
+        self.seq_slots = o; o += _align4(n_seqs)
+        self.seq_start = o; o += _align4(n_seqs + 1)
+        self.seq_pos0 = o; o += _align4(n_seqs)
+        self.want_rows = o; o += _align4(max(n_want, 1))
+        self.tables = []
+        for _ in range(n_groups):
+            self.tables.append(o); o += _align4(n_seqs * pages_per_slot)
+        self.total = o
+
+
+class Engine:
+    """Weights, cache, scratch and stream state of one model on one GPU."""
+
+    def __init__(self, model: Model, config, max_tokens: int, max_seq_len: Optional[int] = None,
+                 n_slots: Optional[int] = None):
+        if model.dtype is None:
+            raise ValueError("the model has no weights bound")
+        self.model, self.config, self.plan = model, config, model.plan
+        self.dtype, self.device = model.dtype, model.device
+        if self.device.type != "cuda":
+            raise KernelBuildError("the engine runs on a CUDA device only; there is no CPU path")
+        max_seq_len = min(max_seq_len or self.plan.max_positions, self.plan.max_positions)
+        self.cache = KVCache(model.cache_needs(), max_tokens, max_seq_len, self.dtype, self.device, n_slots,
+                             cache_from=model.cache_sources())
+        self.max_seq_len = self.cache.max_seq_len
+        self.vocab_size = self.plan.vocab_size
+        self.scratch = Scratch(self.device)
+        self._meta_dev = torch.empty(0, dtype=torch.int32, device=self.device)
+        self._meta_host = [torch.empty(0, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._meta_events = [None, None]
+        self._meta_turn = 0
+        self.kernel_launch_hook = None
+
+    # -- construction
+    @classmethod
+    def from_folder(cls, folder: str, dtype=None, max_tokens: int = 4096, max_seq_len: Optional[int] = None,
+                    device="cuda:0", n_slots: Optional[int] = None) -> "Engine":
+        """Load config.json and the safetensors of `folder`; the model class is chosen by config.json."""
+        config = load_config(folder)
+        model = build_model(config.plan())
+        weights = load_weights(folder, model.weight_specs(), model.ignorable_names())
+        compute = DTYPES[dtype] if dtype is not None else DTYPES[getattr(config, "torch_dtype", "bfloat16")]
+        model.bind(weights, compute, device)
+        return cls(model, config, max_tokens, max_seq_len, n_slots)
+
+    @classmethod
+    def from_random(cls, config, seed: int, dtype=None, max_tokens: int = 4096, max_seq_len: Optional[int] = None,
+                    device="cuda:0", n_slots: Optional[int] = None) -> "Engine":
+        """Seeded random weights drawn on the device (no folder is written)."""
+        plan = config.plan()
+        model = build_model(plan)
+        compute = DTYPES[dtype] if dtype is not None else DTYPES[getattr(config, "torch_dtype", "bfloat16")]
+        weights = random_weights(model.weight_specs(), seed, dtype=compute, device=device)
+        model.bind(weights, compute, device)
+        return cls(model, config, max_tokens, max_seq_len, n_slots)
+
+    # -- sequences
+    def new_sequence(self) -> int:
+        """A free slot for a sequence that starts now (length 0, state zeroed)."""
+        return self.cache.alloc_slot()
+
+    def release(self, slot: int) -> None:
+        """The sequence is finished: its slot and pages are given back."""
+        self.cache.free_slot(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # -- the step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the given tokens of every entry as one batch, append them to the cache and return
+        float32 logits [wanted, vocab] in the order of the entries and of their `want` (None if
+        nothing is wanted).  The tensor is scratch: it is valid until the next step."""
+        ctx = self._prepare(entries)
+        logits = self.model.forward(ctx, self.cache)
+        self.cache.commit(list(zip(ctx.host_slots, ctx.host_n_new)))
+        return logits
+
+    def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+        if not entries:
+            raise StepError("a step needs at least one sequence")
+        slots, n_new, tokens, want_rows = [], [], [], []
+        start = 0
+        for e in entries:
+            toks = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
+            if toks.size == 0:
+                raise StepError(f"slot {e.slot}: a step needs at least one token per sequence")
+            if toks.min() < 0 or toks.max() >= self.vocab_size:
+                raise StepError(f"slot {e.slot}: token id outside the vocabulary [0, {self.vocab_size})")
+            for w in e.want:
+                if not 0 <= int(w) < toks.size:
+                    raise StepError(f"slot {e.slot}: wanted place {w} is outside its {toks.size} tokens")
+                want_rows.append(start + int(w))
+            slots.append(int(e.slot)); n_new.append(int(toks.size)); tokens.append(toks)
+            start += toks.size
+        self.cache.reserve(list(zip(slots, n_new)))       # raises before anything is launched
+        pos0 = [self.cache.length(s) for s in slots]
+        return self._build_context(slots, n_new, pos0, np.concatenate(tokens), want_rows)
+
+    def _build_context(self, slots, n_new, pos0, token_ids, want_rows) -> StepContext:
+        B, N, R = len(slots), int(token_ids.size), len(want_rows)
+        G, P = len(self.cache.groups), self.cache.pages_per_slot
+        lay = _MetaLayout(N, B, R, G, P)
+        turn = self._meta_turn
+        self._meta_turn ^= 1
+        if self._meta_events[turn] is not None:
+            self._meta_events[turn].synchronize()     # the copy that last used this staging buffer is done
+        if self._meta_host[turn].numel() < lay.total:
+            self._meta_host[turn] = torch.empty(max(lay.total, 2 * self._meta_host[turn].numel()),
+                                                dtype=torch.int32).pin_memory()
+        if self._meta_dev.numel() < lay.total:
+            self._meta_dev = torch.empty(max(lay.total, 2 * self._meta_dev.numel()), dtype=torch.int32,
+                                         device=self.device)
+        host = self._meta_host[turn].numpy()
+        n_new_a, pos0_a = np.asarray(n_new, dtype=np.int64), np.asarray(pos0, dtype=np.int64)
+        seq_start = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(n_new_a, out=seq_start[1:])
+        token_seq = np.repeat(np.arange(B, dtype=np.int64), n_new_a)
+        token_pos = np.arange(N, dtype=np.int64) - seq_start[:-1][token_seq] + pos0_a[token_seq]
+        host[lay.token_ids:lay.token_ids + N] = token_ids
+        host[lay.token_seq:lay.token_seq + N] = token_seq
+        host[lay.token_pos:lay.token_pos + N] = token_pos
+        host[lay.seq_slots:lay.seq_slots + B] = slots
+        host[lay.seq_start:lay.seq_start + B + 1] = seq_start
+        host[lay.seq_pos0:lay.seq_pos0 + B] = pos0_a
+        host[lay.want_rows:lay.want_rows + R] = want_rows
+        for g in range(G):
+            host[lay.tables[g]:lay.tables[g] + B * P] = self.cache.page_rows(g, slots).reshape(-1)
+        dev = self._meta_dev
+        dev[:lay.total].copy_(self._meta_host[turn][:lay.total], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self._meta_events[turn] = event
+        return StepContext(
+            n_tokens=N, n_seqs=B, n_want=R, is_decode=bool(n_new_a.max() == 1), max_new=int(n_new_a.max()),
+            max_context=int((pos0_a + n_new_a).max()), max_positions=self.max_seq_len, dtype=self.dtype, device=self.device, scratch=self.scratch,
+            token_ids=dev[lay.token_ids:lay.token_ids + N], token_seq=dev[lay.token_seq:lay.token_seq + N],
+            token_pos=dev[lay.token_pos:lay.token_pos + N], seq_slots=dev[lay.seq_slots:lay.seq_slots + B],
+            seq_start=dev[lay.seq_start:lay.seq_start + B + 1], seq_pos0=dev[lay.seq_pos0:lay.seq_pos0 + B],
+            want_rows=dev[lay.want_rows:lay.want_rows + max(R, 1)],
+            page_tables=[dev[lay.tables[g]:lay.tables[g] + B * P].view(B, P) for g in range(G)],
+            host_slots=list(slots), host_n_new=list(n_new), host_pos0=list(pos0))

@@ -1,0 +1,117 @@
+"""Grouped-query attention over the paged cache, as a mixer part.
+
+Order of operations as in the reference (src/model/self_attention.cpp:122-169):
+q/k/v projections -> per-head RMSNorm of q and k -> rotation -> cache write ->
+causal attention over the cache (scale d^-0.5 after the dot, 32-bit softmax) ->
+output projection.  The three projections run as one product over the row-wise
+concatenation [Wq; Wk; Wv] made at bind time; norm, rotation and the cache write are
+one kernel.  Head counts, head size, scale, window, norm and position encoding are
+parameters; the part does not know its model.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..cache.book import CacheNeed
+from ..config.plan import PartSpec
+from ..csrc import ops
+from ..weights.loader import WeightSpec
+from .base import Part, build_part, register_part
+from .linear import linear
+
+# Hand-written bfloat16 kernels register themselves here: fn(part, q, cache, out, ctx, table) -> bool
+PREFILL_KERNELS = []
+DECODE_KERNELS = []
+
+
+class GQAAttention(Part):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                 qk_norm: Optional[PartSpec] = None, position: Optional[PartSpec] = None,
+                 window: Optional[int] = None, prefix: str = ""):
+        if num_heads % num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if head_dim % 16 or head_dim > 256:
+            raise ValueError(f"head_dim {head_dim}: the attention kernels take multiples of 16 up to 256")
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
+        self.scale, self.window, self.prefix = float(scale), window, prefix
+        self.q_norm = build_part("norm", qk_norm) if qk_norm else None
+        self.k_norm = build_part("norm", qk_norm) if qk_norm else None
+        self.position = build_part("position", position) if position else None
+        self.w_qkv = self.w_o = None
+
+    # -- weights
+    def weight_specs(self, prefix: str) -> dict:
+        p = prefix + self.prefix
+        nq, nkv, d, H = self.num_heads, self.num_kv_heads, self.head_dim, self.hidden_size
+        specs = {p + "q_proj.weight": WeightSpec((nq * d, H)), p + "k_proj.weight": WeightSpec((nkv * d, H)),
+                 p + "v_proj.weight": WeightSpec((nkv * d, H)), p + "o_proj.weight": WeightSpec((H, nq * d))}
+        if self.q_norm is not None:
+            specs.update(self.q_norm.weight_specs(p + "q_norm.weight"))
+            specs.update(self.k_norm.weight_specs(p + "k_norm.weight"))
+        return specs
+
+    def bind(self, weights: dict, prefix: str, dtype, device) -> None:
+        p = prefix + self.prefix
+        self.w_qkv = torch.cat([weights.pop(p + "q_proj.weight"), weights.pop(p + "k_proj.weight"),
+                                weights.pop(p + "v_proj.weight")], dim=0).contiguous()
+        self.w_o = weights.pop(p + "o_proj.weight").contiguous()
+        if self.q_norm is not None:
+            self.q_norm.bind(weights, p + "q_norm.weight", dtype, device)
+            self.k_norm.bind(weights, p + "k_norm.weight", dtype, device)
+
+    # -- cache
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed("window" if self.window else "full", self.num_kv_heads, self.head_dim, self.window)
+
+    # -- step
+    def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+        N = ctx.n_tokens
+        table = ctx.page_tables[cache.group]
+        qkv = ctx.scratch.get("attn.qkv", (N, (nq + 2 * nkv) * d), ctx.dtype)
+        linear(x, self.w_qkv, qkv)
+        q = ctx.scratch.get("attn.q", (N, nq * d), ctx.dtype)
+        norm_eps = self.q_norm.eps if self.q_norm is not None else 0.0
+        qw = self.q_norm.weight if self.q_norm is not None else None
+        kw = self.k_norm.weight if self.k_norm is not None else None
+        if self.position is None or getattr(self.position, "fused_tables", False):
+            cos = sin = None
+            if self.position is not None:
+                self.position.prepare(ctx.max_positions, ctx.device)
+                cos, sin = self.position.cos, self.position.sin
+            ops.qkv_prepare(qkv, q, cache.keys, cache.values, qw, kw, cos, sin, ctx.token_seq, ctx.token_pos, table,
+                            N, nq, nkv, d, norm_eps)
+        else:
+            self._prepare_unfused(qkv, q, cache, ctx, table, qw, kw, norm_eps)
+        attn = ctx.scratch.get("attn.ctx", (N, nq * d), ctx.dtype)
+        self.attend(q, cache, attn, ctx, table)
+        out = ctx.scratch.get("mixer.out", (N, self.hidden_size), ctx.dtype)
+        return linear(attn, self.w_o, out)
+
+    def attend(self, q, cache, out, ctx, table) -> None:
+        if ctx.dtype == torch.bfloat16:
+            for kernel in (DECODE_KERNELS if ctx.is_decode else PREFILL_KERNELS):
+                if kernel(self, q, cache, out, ctx, table):
+                    return
+        ops.attention_generic(q, cache.keys, cache.values, out, ctx.token_seq, ctx.token_pos, table, ctx.n_tokens,
+                              self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window)
+
+    def _prepare_unfused(self, qkv, q, cache, ctx, table, qw, kw, eps) -> None:
+        """A position encoding without kernel tables: norm, then `apply_`, then the cache write."""
+        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+        N = ctx.n_tokens
+        qs = qkv[:, :nq * d].contiguous().view(N, nq, d)
+        ks = qkv[:, nq * d:(nq + nkv) * d].contiguous().view(N, nkv, d)
+        if qw is not None:
+            ops.rms_norm(qs, qw, eps, qs)
+            ops.rms_norm(ks, kw, eps, ks)
+        self.position.prepare(ctx.max_positions, ctx.device)
+        self.position.apply_(qs, ks, ctx.token_pos[:N])
+        packed = torch.cat([qs.view(N, -1), ks.view(N, -1), qkv[:, (nq + nkv) * d:]], dim=1).contiguous()
+        ops.qkv_prepare(packed, q, cache.keys, cache.values, None, None, None, None, ctx.token_seq, ctx.token_pos,
+                        table, N, nq, nkv, d, 0.0)
+
+
+register_part("mixer", "gqa_attention", GQAAttention)

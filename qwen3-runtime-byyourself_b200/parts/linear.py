@@ -1,0 +1,42 @@
+"""y = x . W^T for weights stored [out, in], the one matrix product of the model.
+
+32-bit operands go to the library's own fmaf kernel (true 32-bit, fixed summation
+order).  bfloat16 operands go to the cuBLAS product that torch wraps, as the
+reference's engine does for every projection (src/ops/linear.cpp:165-193:
+cublasGemmEx, bfloat16 in, 32-bit accumulate), unless a hand-written kernel is
+registered for the shape (`set_bf16_kernel`).
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+
+from ..csrc import ops
+
+_bf16_kernel: Optional[Callable] = None
+
+
+def set_bf16_kernel(fn: Optional[Callable]) -> None:
+    """`fn(x, w, out) -> bool` may take a bfloat16 product; False hands it to the library."""
+    global _bf16_kernel
+    _bf16_kernel = fn
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T; out is float32 or x's type."""
+    if x.dtype == torch.float32:
+        if out.dtype != torch.float32:
+            raise ops.KernelError("a 32-bit product writes 32-bit output")
+        return ops.gemm_f32(x, w, out)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise ops.KernelError(f"linear: unsupported operand types {x.dtype}, {w.dtype}")
+    if not x.is_cuda:
+        raise ops.KernelError("linear: CUDA tensors only")
+    if _bf16_kernel is not None and _bf16_kernel(x, w, out):
+        return out
+    if out.dtype == torch.bfloat16:
+        torch.mm(x, w.t(), out=out)
+    else:
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+    return out

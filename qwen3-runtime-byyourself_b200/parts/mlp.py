@@ -1,0 +1,43 @@
+"""SwiGLU feed-forward as a part: down( silu(gate(x)) * up(x) ).
+
+Reference: src/model/mlp.cpp:101-115 (three products and one elementwise kernel) and
+src/ops/elementwise.cu:47-65.  Here gate and up run as one product over the row-wise
+concatenation [Wg; Wu] made at bind time.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from ..weights.loader import WeightSpec
+from .base import Part, register_part
+from .linear import linear
+
+
+class SwiGLU(Part):
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = ""):
+        self.hidden_size, self.intermediate_size, self.prefix = int(hidden_size), int(intermediate_size), prefix
+        self.w_gate_up = self.w_down = None
+
+    def weight_specs(self, prefix: str) -> dict:
+        p, H, I = prefix + self.prefix, self.hidden_size, self.intermediate_size
+        return {p + "gate_proj.weight": WeightSpec((I, H)), p + "up_proj.weight": WeightSpec((I, H)),
+                p + "down_proj.weight": WeightSpec((H, I))}
+
+    def bind(self, weights: dict, prefix: str, dtype, device) -> None:
+        p = prefix + self.prefix
+        self.w_gate_up = torch.cat([weights.pop(p + "gate_proj.weight"), weights.pop(p + "up_proj.weight")],
+                                   dim=0).contiguous()
+        self.w_down = weights.pop(p + "down_proj.weight").contiguous()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        N, I = ctx.n_tokens, self.intermediate_size
+        gate_up = ctx.scratch.get("ff.gate_up", (N, 2 * I), ctx.dtype)
+        linear(x, self.w_gate_up, gate_up)
+        act = ctx.scratch.get("ff.act", (N, I), ctx.dtype)
+        ops.silu_mul(gate_up, act)
+        out = ctx.scratch.get("ff.out", (N, self.hidden_size), ctx.dtype)
+        return linear(act, self.w_down, out)
+
+
+register_part("feed_forward", "swiglu", SwiGLU)

@@ -1,0 +1,67 @@
+"""Chooses the next token of every row on the GPU and brings back only the ids.
+
+Greedy: the argmax kernel.  Sample: the temperature / top-k / top-p kernel, with one
+random stream per sequence keyed by (seed, sequence id, step).  The reference's
+sampler copies the logits to the host and walks them there
+(src/generation/sampler.cpp:277-313); its options and their meaning are kept.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import torch
+
+from ..csrc import ops
+from .params import SamplingParams
+
+
+class NonFiniteLogits(RuntimeError):
+    """A row of logits held NaN or Inf (the reference refuses such rows too)."""
+
+
+class Sampler:
+    def __init__(self, params: SamplingParams, vocab_size: int, device):
+        if params.valid_vocab_size > vocab_size:
+            raise ValueError("valid_vocab_size exceeds logits vocabulary size")
+        if params.mode == "sample" and params.top_k > vocab_size:
+            raise ValueError("top_k exceeds the vocabulary size")
+        self.params, self.vocab_size, self.device = params, vocab_size, torch.device(device)
+        self._cap = 0
+        self._grow(8)
+
+    def _grow(self, rows: int) -> None:
+        if rows <= self._cap:
+            return
+        self._cap = max(rows, 2 * self._cap)
+        self._out = torch.empty(self._cap, dtype=torch.int32, device=self.device)
+        self._ids_dev = torch.empty(self._cap, dtype=torch.int64, device=self.device)
+        self._steps_dev = torch.empty(self._cap, dtype=torch.int32, device=self.device)
+        self._ids_host = torch.empty(self._cap, dtype=torch.int64).pin_memory()
+        self._steps_host = torch.empty(self._cap, dtype=torch.int32).pin_memory()
+        self._out_host = torch.empty(self._cap, dtype=torch.int32).pin_memory()
+
+    def choose_device(self, logits: torch.Tensor, sequence_ids: Sequence[int], steps: Sequence[int]) -> torch.Tensor:
+        """int32 ids [rows] on the device; `sequence_ids[r]`/`steps[r]` key row r's random stream."""
+        rows = logits.shape[0]
+        self._grow(rows)
+        valid = self.params.valid_vocab_size or logits.shape[1]
+        out = self._out[:rows]
+        if self.params.mode == "greedy":
+            return ops.argmax(logits, out, valid)
+        self._ids_host[:rows] = torch.as_tensor(list(sequence_ids), dtype=torch.int64)
+        self._steps_host[:rows] = torch.as_tensor(list(steps), dtype=torch.int32)
+        self._ids_dev[:rows].copy_(self._ids_host[:rows], non_blocking=True)
+        self._steps_dev[:rows].copy_(self._steps_host[:rows], non_blocking=True)
+        p = self.params
+        return ops.sample(logits, out, p.temperature, p.top_k, p.top_p, p.seed, self._ids_dev[:rows],
+                          self._steps_dev[:rows], valid)
+
+    def choose(self, logits: torch.Tensor, sequence_ids: Sequence[int], steps: Sequence[int]) -> List[int]:
+        """The chosen ids as Python ints (one device-to-host copy of 4 bytes per row)."""
+        rows = logits.shape[0]
+        out = self.choose_device(logits, sequence_ids, steps)
+        self._out_host[:rows].copy_(out, non_blocking=False)
+        ids = self._out_host[:rows].tolist()
+        if any(i < 0 for i in ids):
+            raise NonFiniteLogits("sampling met a non-finite logit")
+        return ids

@@ -1,0 +1,182 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16, under every
+way of cutting the same requests into steps: whole; the last 32 tokens one by one;
+batches of unequal lengths whose shorter requests end earlier, one batch after another
+so that slots and pages are used again; long decoding; the first tokens of a sequence."""
+import numpy as np
+import pytest
+
+import schedules
+from helpers import FP32_TOL, bf16_tolerance, make_folder, plain_logits, random_tokens, tiny
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+
+
+def run_steps(engine, steps, rows):
+    """Drive `engine.step` with trace-format steps; returns {(request id, position): logits row}."""
+    from qwen3_b200 import StepEntry
+    slots, got = {}, {}
+    for step, out in zip(steps, rows):
+        entries = []
+        for e in step["entries"]:
+            if e["id"] not in slots:
+                slots[e["id"]] = engine.new_sequence()
+            entries.append(StepEntry(slots[e["id"]], e["tokens"], e["want"]))
+        logits = engine.step(entries)
+        if out:
+            block = logits.cpu().numpy()
+            assert block.shape[0] == len(out)
+            for key, row in zip(out, block):
+                got[key] = row.copy()
+        else:
+            assert logits is None
+        for rid in step["end"]:
+            engine.release(slots.pop(rid))
+    assert not slots
+    return got
+
+
+def check(got, requests, cfg, weights, dtype, label):
+    worst = 0.0
+    for rid, toks in requests.items():
+        exact = plain_logits(cfg, weights, toks)
+        tol = FP32_TOL if dtype == "float32" else bf16_tolerance(cfg, weights, toks, exact)
+        for p in range(len(toks)):
+            if (rid, p) not in got:
+                continue
+            err = float(np.max(np.abs(got[(rid, p)] - exact[p])))
+            worst = max(worst, err)
+            assert np.all(np.isfinite(got[(rid, p)])), f"{label}: request {rid} position {p}: non-finite logits"
+            assert err <= tol, (f"{label} [{dtype}]: request {rid} position {p} of {len(toks)}: "
+                                f"max abs err {err:.3e} > {tol:.3e}")
+    return worst
+
+
+def make_requests(cfg, lengths, seed):
+    rng = np.random.default_rng(seed)
+    return {f"r{i}": random_tokens(rng, n, cfg["vocab_size"]) for i, n in enumerate(lengths)}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = tmp_path_factory.mktemp("models")
+    return {name: make_folder(base, tiny(name), seed=11 + i, name=name) for i, name in enumerate("ABC")}
+
+
+def engine_for(folder, dtype, max_tokens):
+    from qwen3_b200 import Engine
+    return Engine.from_folder(folder, dtype=dtype, max_tokens=max_tokens)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,lengths", [("A", [5, 17, 1, 64, 65, 100]), ("B", [1, 9, 33, 64, 130]),
+                                          ("C", [2, 63, 129, 300])])
+def test_whole_requests(folders, name, lengths, dtype):
+    folder, weights = folders[name]
+    cfg = tiny(name)
+    requests = make_requests(cfg, lengths, seed=1)
+    steps, rows = schedules.whole(requests)
+    engine = engine_for(folder, dtype, schedules.peak_tokens(steps))
+    got = run_steps(engine, steps, rows)
+    assert len(got) == sum(lengths)
+    check(got, requests, cfg, weights, dtype, "whole")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,lengths", [("A", [5, 40, 100]), ("B", [33, 64, 97, 200]), ("C", [31, 32, 33, 257])])
+def test_last_32_tokens_one_by_one(folders, name, lengths, dtype):
+    folder, weights = folders[name]
+    cfg = tiny(name)
+    requests = make_requests(cfg, lengths, seed=2)
+    steps, rows = schedules.tail_one_by_one(requests, 32)
+    engine = engine_for(folder, dtype, schedules.peak_tokens(steps))
+    got = run_steps(engine, steps, rows)
+    check(got, requests, cfg, weights, dtype, "tail one by one")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,lengths,prompts,batch", [
+    ("A", [13, 25, 9, 70, 66, 20, 128, 3], [5, 17, 1, 64, 65, 12, 100, 3], 3),
+    ("B", [13, 21, 45, 76, 30, 200, 65], [1, 9, 33, 64, 30, 129, 2], 4),
+    ("C", [200, 90, 300, 64, 150], [100, 63, 257, 1, 64], 2),
+])
+def test_unequal_batches_one_after_another(folders, name, lengths, prompts, batch, dtype):
+    folder, weights = folders[name]
+    cfg = tiny(name)
+    requests = make_requests(cfg, lengths, seed=3)
+    prompt_lengths = {rid: p for rid, p in zip(requests, prompts)}
+    steps, rows = schedules.batched(requests, prompt_lengths, batch, want_all_prompt=True)
+    # the cache holds exactly what the largest batch needs: later batches reuse slots and pages
+    engine = engine_for(folder, dtype, schedules.peak_tokens(steps))
+    got = run_steps(engine, steps, rows)
+    assert len(got) == sum(lengths)
+    check(got, requests, cfg, weights, dtype, "unequal batches")
+    assert engine.cache.pages_held() == 0 and engine.cache.slots.n_free == engine.cache.n_slots
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(folders, dtype):
+    """One sequence decoded token by token from its first token, across many page edges."""
+    folder, weights = folders["C"]
+    cfg = tiny("C")
+    requests = make_requests(cfg, [400], seed=4)
+    steps, rows = schedules.tail_one_by_one(requests, 400)
+    engine = engine_for(folder, dtype, 448)
+    got = run_steps(engine, steps, rows)
+    assert len(got) == 400
+    check(got, requests, cfg, weights, dtype, "long decoding")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_first_tokens_of_a_sequence(folders, name, dtype):
+    """Sequences of one, two and three tokens, alone and together, whole and token by token."""
+    folder, weights = folders[name]
+    cfg = tiny(name)
+    requests = make_requests(cfg, [1, 2, 3], seed=5)
+    engine = engine_for(folder, dtype, 64 * 3)
+    for builder in (schedules.whole, lambda r: schedules.tail_one_by_one(r, 32),
+                    lambda r: schedules.batched(r, {k: 1 for k in r}, 3)):
+        steps, rows = builder(requests)
+        got = run_steps(engine, steps, rows)
+        check(got, requests, cfg, weights, dtype, "first tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_cutting_does_not_change_logits_beyond_rounding(folders, dtype):
+    """The same positions under three cuttings agree with each other much more closely than
+    with the exact model in bfloat16, and to rounding in 32-bit."""
+    folder, weights = folders["B"]
+    cfg = tiny("B")
+    requests = make_requests(cfg, [70, 33, 120], seed=6)
+    engine = engine_for(folder, dtype, 64 * 6)
+    a = run_steps(engine, *schedules.whole(requests))
+    b = run_steps(engine, *schedules.tail_one_by_one(requests, 32))
+    c = run_steps(engine, *schedules.batched(requests, {"r0": 10, "r1": 33, "r2": 64}, 3))
+    for rid, toks in requests.items():
+        # 32-bit: different summation orders only; bfloat16: the yardstick of the comparison with the exact model
+        tol = 2e-5 if dtype == "float32" else bf16_tolerance(cfg, weights, toks, plain_logits(cfg, weights, toks))
+        for other in (b, c):
+            for (r, p), row in other.items():
+                if r == rid:
+                    assert np.max(np.abs(a[(r, p)] - row)) <= tol, (r, p)
+
+
+def test_step_errors_leave_the_cache_unchanged(folders):
+    from qwen3_b200 import CacheFull, StepEntry, StepError
+    folder, _ = folders["A"]
+    engine = engine_for(folder, "float32", 128)
+    s = engine.new_sequence()
+    with pytest.raises(StepError):
+        engine.step([StepEntry(s, [], [])])
+    with pytest.raises(StepError):
+        engine.step([StepEntry(s, [256], [0])])
+    with pytest.raises(StepError):
+        engine.step([StepEntry(s, [1, 2], [2])])
+    with pytest.raises(CacheFull):
+        engine.step([StepEntry(s, list(range(129)), [])])
+    assert engine.length(s) == 0 and engine.cache.pages_held() == 0
+    assert engine.step([StepEntry(s, [1, 2, 3], [])]) is None
+    assert engine.length(s) == 3
+    engine.release(s)

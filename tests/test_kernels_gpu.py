@@ -1,0 +1,299 @@
+"""Each kernel alone against its plain formula, at sizes other than the models' (odd widths,
+widths that are no multiple of the vector size, head sizes 16..256, several group sizes)."""
+import math
+
+import numpy as np
+import pytest
+
+from plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def dev(a, dtype):
+    return torch.as_tensor(np.asarray(a), dtype=torch.float64).to(DT[dtype]).cuda().contiguous()
+
+
+def back(t):
+    return t.detach().to(torch.float64).cpu().numpy()
+
+
+def stored(a, dtype):
+    """The values the device really holds for `a` in `dtype`, as float64."""
+    return back(dev(a, dtype))
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == "float32" else 1.2e-2) * scale
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows,size", [(7, 1000), (3, 1001), (5, 16), (2, 5120), (1, 12)])
+def test_rms_norm_with_and_without_residual(dtype, rows, size):
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(rows * size)
+    x, d = rng.normal(0, 2, (rows, size)), rng.normal(0, 2, (rows, size))
+    w = 1 + rng.normal(0, 0.1, size)
+    eps = 3e-5
+    rnd = plain.identity if dtype == "float32" else plain.round_bf16
+    xs, ds = stored(x, dtype), stored(d, dtype)
+    wd = torch.as_tensor(w, dtype=torch.float32).cuda()
+    wf = wd.double().cpu().numpy()
+    out = torch.empty_like(dev(x, dtype))
+    ops.rms_norm(dev(x, dtype), wd, eps, out)
+    np.testing.assert_allclose(back(out), plain.rms_norm(xs, wf, eps, rnd), atol=tol(dtype, 4), rtol=tol(dtype))
+    xr = dev(x, dtype)
+    ops.rms_norm(xr, wd, eps, out, dev(d, dtype))
+    summed = rnd(xs + ds)
+    np.testing.assert_allclose(back(xr), summed, atol=tol(dtype, 8), rtol=0)
+    np.testing.assert_allclose(back(out), plain.rms_norm(summed, wf, eps, rnd), atol=tol(dtype, 4), rtol=tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden", [64, 100, 7])
+def test_embedding_and_gather(dtype, hidden):
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(hidden)
+    table = rng.normal(0, 1, (37, hidden))
+    ids = rng.integers(0, 37, size=19)
+    td = dev(table, dtype)
+    out = torch.empty(19, hidden, dtype=DT[dtype], device="cuda")
+    ops.embedding(torch.as_tensor(ids, dtype=torch.int32).cuda(), td, out)
+    np.testing.assert_array_equal(back(out), plain.embedding(ids, back(td)))
+    idx = torch.as_tensor([18, 0, 5, 5], dtype=torch.int32).cuda()
+    picked = torch.empty(4, hidden, dtype=DT[dtype], device="cuda")
+    ops.gather_rows(out, idx, picked)
+    np.testing.assert_array_equal(back(picked), back(out)[[18, 0, 5, 5]])
+    delta = dev(rng.normal(0, 1, (19, hidden)), dtype)
+    ops.gather_rows(out, idx, picked, delta)
+    rnd = plain.identity if dtype == "float32" else plain.round_bf16
+    np.testing.assert_allclose(back(picked), rnd((back(out) + back(delta))[[18, 0, 5, 5]]), atol=tol(dtype), rtol=0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows,inter", [(5, 160), (3, 75), (1, 12288)])
+def test_silu_mul(dtype, rows, inter):
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(inter)
+    gu = rng.normal(0, 2, (rows, 2 * inter))
+    gd = dev(gu, dtype)
+    out = torch.empty(rows, inter, dtype=DT[dtype], device="cuda")
+    ops.silu_mul(gd, out)
+    g = back(gd)
+    rnd = plain.identity if dtype == "float32" else plain.round_bf16
+    np.testing.assert_allclose(back(out), plain.silu_multiply(g[:, :inter], g[:, inter:], rnd),
+                               atol=tol(dtype, 2), rtol=tol(dtype))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 45, 67), (37, 130, 64), (64, 64, 16), (65, 63, 129), (3, 301, 80), (130, 7, 1000)])
+def test_gemm_f32_is_true_32_bit(M, N, K):
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(M * N + K)
+    x, w = rng.normal(0, 1, (M, K)), rng.normal(0, 1, (N, K))
+    xd, wd = dev(x, "float32"), dev(w, "float32")
+    out = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ops.gemm_f32(xd, wd, out)
+    exact = back(xd) @ back(wd).T
+    # 32-bit accumulation of K products of unit scale: error ~ K * 2^-24 * |terms|; TF32 would be ~1e-3
+    assert np.max(np.abs(back(out) - exact)) <= 3e-6 * math.sqrt(K) * 4
+    # a row's result does not depend on the other rows of the batch
+    one = torch.empty(1, N, dtype=torch.float32, device="cuda")
+    ops.gemm_f32(xd[M - 1:M].contiguous(), wd, one)
+    assert torch.equal(one[0], out[M - 1])
+
+
+def paged_case(rng, lengths, nkv, d, dtype, n_spare=3):
+    """Random page tables (shuffled pages) for sequences of the given lengths."""
+    pages_per_seq = max(-(-n // 64) for n in lengths)
+    n_pages = sum(-(-n // 64) for n in lengths) + n_spare
+    order = rng.permutation(n_pages)
+    table = np.full((len(lengths), pages_per_seq), -1, dtype=np.int32)
+    k = 0
+    for s, n in enumerate(lengths):
+        for i in range(-(-n // 64)):
+            table[s, i] = order[k]
+            k += 1
+    kp = torch.zeros(n_pages, nkv, 64, d, dtype=DT[dtype], device="cuda")
+    vp = torch.zeros_like(kp)
+    return table, kp, vp
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq,nkv,d", [(4, 2, 16), (8, 1, 32), (6, 3, 48), (8, 2, 128), (2, 2, 256), (5, 5, 80)])
+def test_prepare_and_attention_over_pages(dtype, nq, nkv, d):
+    """Two steps per sequence (a prompt, then more tokens) through qkv_prepare and the attention
+    kernel, over shuffled pages, against per-head norm + rotation + causal attention in float64."""
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(nq * 1000 + d)
+    lengths, first = [70, 5, 129], [64, 1, 100]
+    eps, theta = 2e-5, 12345.0
+    rnd = plain.identity if dtype == "float32" else plain.round_bf16
+    table, kp, vp = paged_case(rng, lengths, nkv, d, dtype)
+    table_d = torch.as_tensor(table).cuda()
+    cos, sin = plain.rope_table(max(lengths), d, theta)
+    cos_d = torch.as_tensor(cos, dtype=torch.float32).cuda()
+    sin_d = torch.as_tensor(sin, dtype=torch.float32).cuda()
+    qw, kw = 1 + rng.normal(0, 0.1, d), 1 + rng.normal(0, 0.1, d)
+    qw_d, kw_d = torch.as_tensor(qw, dtype=torch.float32).cuda(), torch.as_tensor(kw, dtype=torch.float32).cuda()
+    qw, kw = qw_d.double().cpu().numpy(), kw_d.double().cpu().numpy()
+    full = [rng.normal(0, 1, (n, (nq + 2 * nkv) * d)) for n in lengths]
+    got = [np.zeros((n, nq * d)) for n in lengths]
+    for part in range(2):
+        spans = [(0, f) if part == 0 else (f, n) for f, n in zip(first, lengths)]
+        rows = np.concatenate([full[s][a:b] for s, (a, b) in enumerate(spans)])
+        seq = np.concatenate([np.full(b - a, s) for s, (a, b) in enumerate(spans)]).astype(np.int32)
+        pos = np.concatenate([np.arange(a, b) for a, b in spans]).astype(np.int32)
+        N = rows.shape[0]
+        qkv = dev(rows, dtype)
+        q = torch.empty(N, nq * d, dtype=DT[dtype], device="cuda")
+        out = torch.empty_like(q)
+        seq_d, pos_d = torch.as_tensor(seq).cuda(), torch.as_tensor(pos).cuda()
+        ops.qkv_prepare(qkv, q, kp, vp, qw_d, kw_d, cos_d, sin_d, seq_d, pos_d, table_d, N, nq, nkv, d, eps)
+        ops.attention_generic(q, kp, vp, out, seq_d, pos_d, table_d, N, nq, nkv, d, d ** -0.5)
+        o = back(out)
+        k = 0
+        for s, (a, b) in enumerate(spans):
+            got[s][a:b] = o[k:k + b - a]
+            k += b - a
+    for s, n in enumerate(lengths):
+        x = stored(full[s], dtype)
+        qs = x[:, :nq * d].reshape(n, nq, d)
+        ks = x[:, nq * d:(nq + nkv) * d].reshape(n, nkv, d)
+        vs = x[:, (nq + nkv) * d:].reshape(n, nkv, d)
+        pos = np.arange(n)
+        qs = plain.apply_rope(plain.rms_norm(qs, qw, eps, rnd), pos, cos, sin, rnd)
+        ks = plain.apply_rope(plain.rms_norm(ks, kw, eps, rnd), pos, cos, sin, rnd)
+        want = plain.gqa_attention(qs, ks, vs).reshape(n, nq * d)
+        err = np.max(np.abs(got[s] - want))
+        assert err <= tol(dtype, 3), f"sequence {s}: max abs err {err:.3e}"
+        # the cache holds the rotated keys and the raw values at the right page and row
+        for p in (0, n - 1, min(n - 1, 64)):
+            page = table[s, p // 64]
+            np.testing.assert_allclose(back(kp[page, :, p % 64, :]), ks[p], atol=tol(dtype, 3), rtol=0)
+            np.testing.assert_array_equal(back(vp[page, :, p % 64, :]), vs[p])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    """One early key is made to dominate one late query: the output must be that key's value.
+    Random keys alone would hide a kernel that skips a page or reads a wrong row."""
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(5)
+    nq, nkv, d, n = 4, 2, 32, 600
+    for far in (3, 64, 127, 320, 598):
+        table, kp, vp = paged_case(rng, [n], nkv, d, dtype)
+        rows = rng.normal(0, 0.3, (n, (nq + 2 * nkv) * d))
+        direction = rng.normal(0, 1, d)
+        direction *= 12.0 / np.linalg.norm(direction)
+        rows[n - 1, 2 * d:3 * d] = direction * 3             # query head 2 (kv head 1) of the last token
+        rows[far, (nq + 1) * d:(nq + 2) * d] = direction * 3    # key of kv head 1 at `far`
+        seq = torch.zeros(n, dtype=torch.int32, device="cuda")
+        pos = torch.arange(n, dtype=torch.int32, device="cuda")
+        q = torch.empty(n, nq * d, dtype=DT[dtype], device="cuda")
+        out = torch.empty_like(q)
+        table_d = torch.as_tensor(table).cuda()
+        ops.qkv_prepare(dev(rows, dtype), q, kp, vp, None, None, None, None, seq, pos, table_d, n, nq, nkv, d, 0.0)
+        ops.attention_generic(q, kp, vp, out, seq, pos, table_d, n, nq, nkv, d, d ** -0.5)
+        x = stored(rows, dtype)
+        value = x[far, (nq + nkv + 1) * d:(nq + nkv + 2) * d]
+        got = back(out)[n - 1, 2 * d:3 * d]
+        assert np.max(np.abs(got - value)) <= 2e-2, f"far key {far}: {np.max(np.abs(got - value)):.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_window_edge(dtype):
+    """With a window of w keys, a dominating key exactly w back is invisible and one w-1 back is seen."""
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(6)
+    nq, nkv, d, n, window = 2, 1, 16, 200, 70
+    for back_by, seen in ((window - 1, True), (window, False)):
+        table, kp, vp = paged_case(rng, [n], nkv, d, dtype)
+        rows = rng.normal(0, 0.3, (n, (nq + 2 * nkv) * d))
+        direction = rng.normal(0, 1, d)
+        direction *= 36.0 / np.linalg.norm(direction)
+        far = n - 1 - back_by
+        rows[n - 1, 0:d] = direction
+        rows[far, nq * d:(nq + 1) * d] = direction
+        seq = torch.zeros(n, dtype=torch.int32, device="cuda")
+        pos = torch.arange(n, dtype=torch.int32, device="cuda")
+        q = torch.empty(n, nq * d, dtype=DT[dtype], device="cuda")
+        out = torch.empty_like(q)
+        table_d = torch.as_tensor(table).cuda()
+        ops.qkv_prepare(dev(rows, dtype), q, kp, vp, None, None, None, None, seq, pos, table_d, n, nq, nkv, d, 0.0)
+        ops.attention_generic(q, kp, vp, out, seq, pos, table_d, n, nq, nkv, d, d ** -0.5, window)
+        x = stored(rows, dtype)
+        qs = x[:, :nq * d].reshape(n, nq, d)
+        ks = x[:, nq * d:(nq + nkv) * d].reshape(n, nkv, d)
+        vs = x[:, (nq + nkv) * d:].reshape(n, nkv, d)
+        want = plain.gqa_attention(qs, ks, vs, window=window).reshape(n, nq * d)
+        assert np.max(np.abs(back(out) - want)) <= tol(dtype, 3)
+        hit = np.max(np.abs(back(out)[n - 1, :d] - vs[far, 0])) <= 2e-2
+        assert hit == seen
+
+
+def test_argmax_lowest_id_among_equals_and_nan():
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(7)
+    logits = rng.normal(0, 1, (6, 1013)).astype(np.float32)
+    logits[0, [400, 17, 900]] = 9.0
+    logits[1, 5] = np.nan
+    logits[2, :] = -np.inf
+    logits[3, 1012] = 50.0
+    logits[4, 0] = 50.0
+    logits[5, 700:] = 100.0            # beyond the valid prefix in the second call
+    d = torch.as_tensor(logits).cuda()
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    ops.argmax(d, out)
+    assert out.tolist() == [plain.argmax_lowest(r) for r in logits]
+    assert out.tolist()[:5] == [17, plain.argmax_lowest(logits[1]), 0, 1012, 0]
+    ops.argmax(d, out, 700)
+    assert out.tolist() == [plain.argmax_lowest(r, 700) for r in logits]
+
+
+@pytest.mark.parametrize("temperature,top_k,top_p", [(0.6, 20, 0.95), (1.0, 0, 1.0), (0.7, 0, 0.9), (1.3, 5, 1.0),
+                                                     (0.2, 1, 0.5), (2.0, 300, 0.3)])
+def test_sampling_kernel_follows_the_reference_order(temperature, top_k, top_p):
+    """The kernel's draw equals the plain walk (temperature -> top-k with ties -> sort -> softmax
+    -> top-p -> inverse CDF) for the same uniform number, on rows with many equal logits."""
+    from qwen3_b200 import uniform_for
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(int(temperature * 10) + top_k)
+    rows, vocab, valid = 24, 1500, 1400
+    logits = rng.normal(0, 2.5, (rows, vocab)).astype(np.float32)
+    logits[::2] = np.round(logits[::2] * 4) / 4          # coarse values: many ties, as bfloat16 logits have
+    logits[:, valid:] = 1e4                              # ids beyond the valid prefix must never be drawn
+    logits[3, :50] = 6.0
+    seed = 42
+    seq_ids = torch.arange(100, 100 + rows, dtype=torch.int64, device="cuda")
+    d = torch.as_tensor(logits).cuda()
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    for step in (0, 1, 7):
+        steps = torch.full((rows,), step, dtype=torch.int32, device="cuda")
+        ops.sample(d, out, temperature, top_k, top_p, seed, seq_ids, steps, valid)
+        got = out.tolist()
+        want = [plain.sample_row(logits[r], np.float32(temperature), top_k, np.float32(top_p),
+                                 uniform_for(seed, 100 + r, step), valid) for r in range(rows)]
+        assert got == want, (step, got, want)
+    bad = logits.copy()
+    bad[2, 7] = np.inf
+    ops.sample(torch.as_tensor(bad).cuda(), out, temperature, top_k, top_p, seed, seq_ids, steps, valid)
+    assert out.tolist()[2] == -1 and out.tolist()[1] == want[1]
+
+
+def test_sampling_statistics_match_the_distribution():
+    """Over many streams the kernel's draws follow softmax(logits / T) restricted by top-k."""
+    from qwen3_b200.csrc import ops
+    logits = np.array([[2.0, 2.0, 1.0, -10.0, 0.5, 0.0, -1.0, 1.5]], dtype=np.float32)
+    n = 4000
+    d = torch.as_tensor(np.repeat(logits, n, axis=0)).cuda()
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    ops.sample(d, out, 0.8, 3, 1.0, 9, torch.arange(n, dtype=torch.int64, device="cuda"),
+               torch.zeros(n, dtype=torch.int32, device="cuda"))
+    counts = np.bincount(out.cpu().numpy(), minlength=8)
+    assert counts[[2, 3, 4, 5, 6]].sum() == 0            # top-3 keeps ids 0, 1 (tie) and 7
+    w = np.exp(np.array([2.0, 2.0, 1.5]) / 0.8)
+    expect = w / w.sum() * n
+    assert np.all(np.abs(counts[[0, 1, 7]] - expect) < 5 * np.sqrt(expect))
