@@ -1,0 +1,285 @@
+"""Benchmark of the library's headline metric: decoded tokens a second of a Qwen3-8B-shaped
+model with random weights in bfloat16 on one B200, batch 8 at a context of 4,096 tokens.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  A "step" is one decode step of the whole batch.
+  value     decoded tokens a second, timed on the device with CUDA events around K steps;
+            each step's next tokens are chosen on the device (greedy) and fed back there
+  e2e       the same through the Python entry point `generate_token_ids`: host token ids in,
+            host token ids out, every step
+  prefill   one prompt of 2,048 tokens in one step: tokens a second, and its flops over the
+            time over the bfloat16 peak
+  roofline  bytes a decode step has to read (every weight it uses once, and the cache of the
+            live requests) over its time, against the measured copy bandwidth
+  points    decoded tokens a second at batch 1 and batch 64 (unequal prompts up to 2,048)
+Peaks are read from MEASURED_PEAKS.json beside this file if it exists, else the stated
+fallback of an earlier measurement on the same pool is used.
+"""
+import argparse
+import dataclasses
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+QWEN3_8B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu", "torch_dtype": "bfloat16",
+    "num_hidden_layers": 36, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 40960,
+    "attention_bias": False, "use_sliding_window": False, "sliding_window": None, "rope_scaling": None,
+    "bos_token_id": 151643, "eos_token_id": 151645,
+}
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            raw = json.load(f)
+        peaks = {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]), "source": "measured"}
+        if "bf16_tflops_sustained" in raw:
+            peaks["bf16_tflops_sustained"] = float(raw["bf16_tflops_sustained"])
+        return peaks
+    except (OSError, KeyError, ValueError, TypeError):
+        return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.samples, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        mhz = [int(s[0]) for s in self.samples if s[0].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None,
+                "sm_max_mhz": int(self.samples[0][1]) if self.samples[0][1].isdigit() else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def unequal_lengths(n, longest, rng):
+    """n prompt lengths between 3/4 of `longest` and `longest`, the longest included."""
+    import numpy as np
+    lengths = rng.integers(max(1, longest * 3 // 4), longest + 1, size=n)
+    lengths[0] = longest
+    return [int(x) for x in lengths]
+
+
+def weight_bytes_per_step(cfg, layers, rows):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = ((nq + 2 * nkv) * d * H + H * nq * d + 3 * H * I) * 2 + (2 * H + 2 * d) * 4
+    return layers * per_layer + V * H * 2 + H * 4 + rows * H * 2   # + lm_head, final norm, embedding rows read
+
+
+def prefill_flops(cfg, layers, T):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    linear = 2 * T * ((nq + 2 * nkv) * d * H + H * nq * d + 3 * H * I)
+    attention = 2 * 2 * nq * d * (T * (T + 1) // 2)          # QK^T and PV over the causal half
+    return layers * (linear + attention) + 2 * V * H          # + the one row of logits that is wanted
+
+
+def decode_run(q, engine, sampler, torch, rng, batch, longest_prompt, steps, warmup, clocks=None):
+    """Prefill `batch` unequal prompts in one step, then time `steps` decode steps on the device."""
+    import numpy as np
+    lengths = unequal_lengths(batch, longest_prompt, rng)
+    slots = [engine.new_sequence() for _ in range(batch)]
+    prompts = [rng.integers(0, engine.vocab_size, size=n).tolist() for n in lengths]
+    # prompts go in slices so that scratch stays small; every slice is a step of unequal lengths
+    chunk = max(1, 8192 // max(lengths))
+    ids = torch.empty(batch, dtype=torch.int32, device=engine.device)
+    for lo in range(0, batch, chunk):
+        part = range(lo, min(batch, lo + chunk))
+        logits = engine.step([q.StepEntry(slots[i], prompts[i], [len(prompts[i]) - 1]) for i in part])
+        ids[lo:lo + len(part)] = sampler.choose_device(logits, list(part), [0] * len(part))
+    entries = [q.StepEntry(s, [0], [0]) for s in slots]
+    seq_ids = list(range(batch))
+
+    def one(step_index):
+        logits = engine.step(entries, device_tokens=ids)
+        ids.copy_(sampler.choose_device(logits, seq_ids, [step_index] * batch))
+
+    for i in range(warmup):
+        one(1 + i)
+    torch.cuda.synchronize()
+    launches_before = engine.launches
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if clocks is not None:
+        clocks.__enter__()
+    start.record()
+    for i in range(steps):
+        one(1 + warmup + i)
+    stop.record()
+    torch.cuda.synchronize()
+    if clocks is not None:
+        clocks.__exit__()
+    ms = start.elapsed_time(stop) / steps
+    cached = sum(engine.length(s) for s in slots) - batch * steps / 2.0      # mean over the timed steps
+    launches = (engine.launches - launches_before) + steps                     # + the sampler's kernel
+    for s in slots:
+        engine.release(s)
+    return {"ms": ms, "tok_s": batch / ms * 1e3, "cached_tokens": cached, "launches": launches,
+            "longest": max(lengths) + warmup + steps}
+
+
+def e2e_run(q, engine, torch, rng, batch, longest_prompt, steps, warmup):
+    """Through `generate_token_ids`: host prompts in, host token ids out; the decode steps after
+    the warm-up are timed on the host clock (each ends with the device-to-host read of its ids)."""
+    lengths = unequal_lengths(batch, longest_prompt, rng)
+    prompts = [rng.integers(0, engine.vocab_size, size=n).tolist() for n in lengths]
+    marks = []
+
+    def on_token(index, token):
+        if index == 0:
+            marks.append(time.perf_counter())
+
+    q.generate_token_ids(engine, prompts, q.SamplingParams(mode="greedy"),
+                         q.GenerationOptions(max_new_tokens=1 + warmup + steps), on_token=on_token)
+    torch.cuda.synchronize()
+    # marks[k] is taken after step k's ids reached the host; step 0 is the prefill
+    seconds = marks[warmup + steps] - marks[warmup]
+    return {"tok_s": batch * steps / seconds, "ms": seconds / steps * 1e3}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (both are reported)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a CMake C++/CUDA project without a Python package and its src/core and "
+                          "include/qwen3/core are absent from the checkout, so it neither installs nor compiles"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import numpy as np
+    import torch
+    import qwen3_b200 as q
+    from qwen3_b200.sampling.sampler import Sampler
+
+    cfg = dict(QWEN3_8B)
+    layers = args.layers or cfg["num_hidden_layers"]
+    config = q.config_from_dict(dict(cfg, num_hidden_layers=layers))
+    peaks = load_peaks()
+    rng = np.random.default_rng(0)
+    torch.cuda.set_device(0)
+    batch = args.batch
+    max_batch = batch if args.skip_points else max(batch, 64)
+    engine = q.Engine.from_random(config, seed=0, dtype="bfloat16", max_tokens=max_batch * CONTEXT,
+                                  max_seq_len=CONTEXT)
+    sampler = Sampler(q.SamplingParams(mode="greedy"), engine.vocab_size, engine.device)
+
+    # headline: batch 8 whose longest sequence ends at the context length
+    clocks = ClockSampler()
+    head = decode_run(q, engine, sampler, torch, rng, batch, CONTEXT - warmup - args.steps - 1, args.steps, warmup, clocks)
+    step_bytes = weight_bytes_per_step(cfg, layers, batch) + head["cached_tokens"] * engine.cache.bytes_per_token()
+    achieved = step_bytes / (head["ms"] * 1e-3) / 1e9
+    e2e = e2e_run(q, engine, torch, rng, batch, CONTEXT - warmup - args.steps - 1, args.steps, warmup)
+    h2d = engine.last_upload_bytes
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            r = decode_run(q, engine, sampler, torch, rng, b, 2048, min(args.steps, 32), warmup)
+            points[f"decode_b{b}"] = round(r["tok_s"], 1)
+
+    # prefill: one prompt of 2,048 tokens in one step
+    times = []
+    for rep in range(2 + 3):
+        slot = engine.new_sequence()
+        prompt = rng.integers(0, engine.vocab_size, size=PREFILL_TOKENS).tolist()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        engine.step([q.StepEntry(slot, prompt, [PREFILL_TOKENS - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        engine.release(slot)
+        if rep >= 2:
+            times.append(start.elapsed_time(stop))
+    prefill_ms = statistics.median(times)
+    flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
+
+    line = {
+        "metric": "decode tok/s at batch 8, context 4096 (Qwen3-8B shape, random weights, 1 B200)",
+        "value": round(head["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(head["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights, uniform-random token ids", "impl": "ours",
+        "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_of_config": cfg["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": batch,
+                   "seq_len": CONTEXT, "longest_context_reached": head["longest"], "parallelism": "none (1 GPU)",
+                   "cache": "paged, 64 tokens a page", "l2": "a step reads >15 GB of weights, far above the 126 MB L2",
+                   "sampling": "greedy on the device"},
+        "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms"], 4),
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4 * batch},
+        "gpu_launches": int(head["launches"]),
+        "prefill": {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4), "peaks": peaks["source"]},
+        "points": points,
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

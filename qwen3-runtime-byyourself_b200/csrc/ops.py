@@ -37,7 +37,17 @@ def _fn(source: str, name: str, argtypes, defines=()):
     return fn
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernels of this library have been launched (or captured into a graph) so far."""
+    return _launches
+
+
 def _check(code: int, name: str):
+    global _launches
+    _launches += 1
     if code != 0:
         what = _ERRORS.get(code)
         if what is None:

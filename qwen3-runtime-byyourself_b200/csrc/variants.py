@@ -1,0 +1,11 @@
+"""Every (source, definitions) pair that the library can ask the compiler for with the
+head sizes of the shipped configurations; `build()` of the build driver compiles them all."""
+
+
+def all_variants():
+    return [
+        ("elementwise.cu", ()),
+        ("gemm_f32.cu", ()),
+        ("attention.cu", ()),
+        ("sampling.cu", ()),
+    ]

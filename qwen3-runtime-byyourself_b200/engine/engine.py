@@ -66,11 +66,114 @@ class _MetaLayout:
         self.total = o
 
 
+class _MetaBuffer:
+    """A device int32 buffer with two pinned staging buffers that take turns."""
+
+    def __init__(self, device):
+        self.device = device
+        self.dev = torch.empty(0, dtype=torch.int32, device=device)
+        self._host = [torch.empty(0, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._events = [None, None]
+        self._turn = 0
+
+    def reserve(self, total: int) -> None:
+        if self.dev.numel() < total:
+            self.dev = torch.empty(max(total, 2 * self.dev.numel()), dtype=torch.int32, device=self.device)
+
+    def stage(self, total: int) -> np.ndarray:
+        """A host array of `total` int32 to fill; `upload` then copies it to the device buffer."""
+        turn = self._turn
+        if self._events[turn] is not None:
+            self._events[turn].synchronize()      # the copy that last used this staging buffer is done
+        if self._host[turn].numel() < total:
+            self._host[turn] = torch.empty(max(total, 2 * self._host[turn].numel()), dtype=torch.int32).pin_memory()
+        self.reserve(total)
+        return self._host[turn].numpy()[:total]
+
+    def upload(self, total: int) -> None:
+        turn = self._turn
+        self._turn ^= 1
+        self.dev[:total].copy_(self._host[turn][:total], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self._events[turn] = event
+        self.bytes_last_upload = total * 4
+
+
+def decode_bucket(n: int) -> int:
+    """Fixed batch sizes for captured decode steps: 1..8 exactly, then multiples of 8, of 32 above 64."""
+    if n <= 8:
+        return n
+    if n <= 64:
+        return -(-n // 8) * 8
+    return -(-n // 32) * 32
+
+
+class _DecodeGraph:
+    """One decode step for a fixed number of rows, captured once as a CUDA graph and replayed.
+
+    Rows beyond the live sequences are padding: token 0 at position 0 of the spare page that
+    belongs to no sequence; their logits are computed and dropped, no live row reads them."""
+
+    def __init__(self, engine: "Engine", rows: int):
+        self.engine, self.rows = engine, rows
+        cache = engine.cache
+        G, P = len(cache.groups), cache.pages_per_slot
+        self.layout = _MetaLayout(rows, rows, rows, G, P)
+        self.meta = _MetaBuffer(engine.device)
+        self.meta.reserve(self.layout.total)
+        self.scratch = Scratch(engine.device)
+        self.ctx = engine._context_views(self.meta.dev, self.layout, rows, rows, rows, self.scratch, is_decode=True,
+                                         max_new=1, max_context=engine.max_seq_len)
+        self.graph = None
+        self.logits = None
+        self.launches = 0
+
+    def _fill(self, slots, pos0, token_ids) -> None:
+        lay, rows, B = self.layout, self.rows, len(slots)
+        cache = self.engine.cache
+        host = self.meta.stage(lay.total)
+        host[:] = 0
+        host[lay.token_ids:lay.token_ids + B] = token_ids
+        host[lay.token_seq:lay.token_seq + rows] = np.arange(rows)
+        host[lay.token_pos:lay.token_pos + B] = pos0
+        host[lay.seq_slots:lay.seq_slots + B] = slots
+        host[lay.seq_start:lay.seq_start + rows + 1] = np.arange(rows + 1)
+        host[lay.seq_pos0:lay.seq_pos0 + B] = pos0
+        host[lay.want_rows:lay.want_rows + rows] = np.arange(rows)
+        P = cache.pages_per_slot
+        for g in range(len(cache.groups)):
+            table = host[lay.tables[g]:lay.tables[g] + rows * P].reshape(rows, P)
+            table[:] = cache.n_pages                 # the spare page
+            table[:B] = cache.page_rows(g, slots)
+        self.meta.upload(lay.total)
+
+    def run(self, slots, pos0, token_ids, device_tokens=None) -> torch.Tensor:
+        """Logits [rows, vocab] of the captured step; rows beyond len(slots) are padding."""
+        self._fill(slots, pos0, token_ids)
+        if device_tokens is not None:
+            self.ctx.token_ids[:len(slots)].copy_(device_tokens)
+        if self.graph is None:
+            from ..csrc import ops
+            model, cache = self.engine.model, self.engine.cache
+            model.forward(self.ctx, cache)           # loads kernels and library handles outside the capture
+            torch.cuda.synchronize(self.engine.device)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
+            with torch.cuda.graph(graph):
+                self.logits = model.forward(self.ctx, cache)
+            self.launches = ops.launch_count() - before
+            self.graph = graph
+        self.graph.replay()
+        self.engine.launches += self.launches
+        return self.logits
+
+
 class Engine:
     """Weights, cache, scratch and stream state of one model on one GPU."""
 
     def __init__(self, model: Model, config, max_tokens: int, max_seq_len: Optional[int] = None,
-                 n_slots: Optional[int] = None):
+                 n_slots: Optional[int] = None, use_graphs: bool = True):
         if model.dtype is None:
             raise ValueError("the model has no weights bound")
         self.model, self.config, self.plan = model, config, model.plan
@@ -83,34 +186,33 @@ class Engine:
         self.max_seq_len = self.cache.max_seq_len
         self.vocab_size = self.plan.vocab_size
         self.scratch = Scratch(self.device)
-        self._meta_dev = torch.empty(0, dtype=torch.int32, device=self.device)
-        self._meta_host = [torch.empty(0, dtype=torch.int32).pin_memory() for _ in range(2)]
-        self._meta_events = [None, None]
-        self._meta_turn = 0
-        self.kernel_launch_hook = None
+        self._meta = _MetaBuffer(self.device)
+        self.use_graphs = use_graphs
+        self._graphs = {}
+        self.launches = 0          # kernels of this library launched by steps (replayed graph nodes included)
+        self.last_upload_bytes = 0
 
     # -- construction
     @classmethod
     def from_folder(cls, folder: str, dtype=None, max_tokens: int = 4096, max_seq_len: Optional[int] = None,
-                    device="cuda:0", n_slots: Optional[int] = None) -> "Engine":
+                    device="cuda:0", n_slots: Optional[int] = None, use_graphs: bool = True) -> "Engine":
         """Load config.json and the safetensors of `folder`; the model class is chosen by config.json."""
         config = load_config(folder)
         model = build_model(config.plan())
         weights = load_weights(folder, model.weight_specs(), model.ignorable_names())
         compute = DTYPES[dtype] if dtype is not None else DTYPES[getattr(config, "torch_dtype", "bfloat16")]
         model.bind(weights, compute, device)
-        return cls(model, config, max_tokens, max_seq_len, n_slots)
+        return cls(model, config, max_tokens, max_seq_len, n_slots, use_graphs)
 
     @classmethod
     def from_random(cls, config, seed: int, dtype=None, max_tokens: int = 4096, max_seq_len: Optional[int] = None,
-                    device="cuda:0", n_slots: Optional[int] = None) -> "Engine":
+                    device="cuda:0", n_slots: Optional[int] = None, use_graphs: bool = True) -> "Engine":
         """Seeded random weights drawn on the device (no folder is written)."""
-        plan = config.plan()
-        model = build_model(plan)
+        model = build_model(config.plan())
         compute = DTYPES[dtype] if dtype is not None else DTYPES[getattr(config, "torch_dtype", "bfloat16")]
         weights = random_weights(model.weight_specs(), seed, dtype=compute, device=device)
         model.bind(weights, compute, device)
-        return cls(model, config, max_tokens, max_seq_len, n_slots)
+        return cls(model, config, max_tokens, max_seq_len, n_slots, use_graphs)
 
     # -- sequences
     def new_sequence(self) -> int:
@@ -125,16 +227,14 @@ class Engine:
         return self.cache.length(slot)
 
     # -- the step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run the given tokens of every entry as one batch, append them to the cache and return
         float32 logits [wanted, vocab] in the order of the entries and of their `want` (None if
-        nothing is wanted).  The tensor is scratch: it is valid until the next step."""
-        ctx = self._prepare(entries)
-        logits = self.model.forward(ctx, self.cache)
-        self.cache.commit(list(zip(ctx.host_slots, ctx.host_n_new)))
-        return logits
+        nothing is wanted).  The tensor is scratch: it is valid until the next step.
 
-    def _prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+        `device_tokens` (int32 [len(entries)] on the device) replaces the tokens of a step in which
+        every entry brings one token: the ids are read where the sampler wrote them, and the
+        entries' own tokens only stand for the count."""
         if not entries:
             raise StepError("a step needs at least one sequence")
         slots, n_new, tokens, want_rows = [], [], [], []
@@ -151,25 +251,57 @@ class Engine:
                 want_rows.append(start + int(w))
             slots.append(int(e.slot)); n_new.append(int(toks.size)); tokens.append(toks)
             start += toks.size
-        self.cache.reserve(list(zip(slots, n_new)))       # raises before anything is launched
+        decode = max(n_new) == 1
+        if device_tokens is not None and not decode:
+            raise StepError("device_tokens stand for one token per entry")
+        step = list(zip(slots, n_new))
+        self.cache.reserve(step)                            # raises before anything is launched
         pos0 = [self.cache.length(s) for s in slots]
-        return self._build_context(slots, n_new, pos0, np.concatenate(tokens), want_rows)
+        token_ids = np.concatenate(tokens)
+        if decode and self.use_graphs:
+            logits = self._step_captured(slots, pos0, token_ids, want_rows, device_tokens)
+        else:
+            from ..csrc import ops
+            before = ops.launch_count()
+            ctx = self._build_context(slots, n_new, pos0, token_ids, want_rows)
+            if device_tokens is not None:
+                ctx.token_ids[:len(slots)].copy_(device_tokens)
+            logits = self.model.forward(ctx, self.cache)
+            self.launches += ops.launch_count() - before
+        self.cache.commit(step)
+        return logits
+
+    def _step_captured(self, slots, pos0, token_ids, want_rows, device_tokens):
+        rows = decode_bucket(len(slots))
+        graph = self._graphs.get(rows)
+        if graph is None:
+            graph = self._graphs[rows] = _DecodeGraph(self, rows)
+        logits = graph.run(slots, pos0, token_ids, device_tokens)
+        self.last_upload_bytes = graph.meta.bytes_last_upload
+        if not want_rows:
+            return None
+        if want_rows == list(range(len(want_rows))):
+            return logits[:len(want_rows)]
+        return logits[torch.as_tensor(want_rows, device=self.device)]
+
+    def _context_views(self, dev, lay, N, B, R, scratch, is_decode, max_new, max_context, host=None) -> StepContext:
+        G, P = len(self.cache.groups), self.cache.pages_per_slot
+        return StepContext(
+            n_tokens=N, n_seqs=B, n_want=R, is_decode=is_decode, max_new=max_new, max_context=max_context,
+            max_positions=self.max_seq_len, dtype=self.dtype, device=self.device, scratch=scratch,
+            token_ids=dev[lay.token_ids:lay.token_ids + N], token_seq=dev[lay.token_seq:lay.token_seq + N],
+            token_pos=dev[lay.token_pos:lay.token_pos + N], seq_slots=dev[lay.seq_slots:lay.seq_slots + B],
+            seq_start=dev[lay.seq_start:lay.seq_start + B + 1], seq_pos0=dev[lay.seq_pos0:lay.seq_pos0 + B],
+            want_rows=dev[lay.want_rows:lay.want_rows + max(R, 1)],
+            page_tables=[dev[lay.tables[g]:lay.tables[g] + B * P].view(B, P) for g in range(G)],
+            host_slots=list(host[0]) if host else [], host_n_new=list(host[1]) if host else [],
+            host_pos0=list(host[2]) if host else [])
 
     def _build_context(self, slots, n_new, pos0, token_ids, want_rows) -> StepContext:
         B, N, R = len(slots), int(token_ids.size), len(want_rows)
         G, P = len(self.cache.groups), self.cache.pages_per_slot
         lay = _MetaLayout(N, B, R, G, P)
-        turn = self._meta_turn
-        self._meta_turn ^= 1
-        if self._meta_events[turn] is not None:
-            self._meta_events[turn].synchronize()     # the copy that last used this staging buffer is done
-        if self._meta_host[turn].numel() < lay.total:
-            self._meta_host[turn] = torch.empty(max(lay.total, 2 * self._meta_host[turn].numel()),
-                                                dtype=torch.int32).pin_memory()
-        if self._meta_dev.numel() < lay.total:
-            self._meta_dev = torch.empty(max(lay.total, 2 * self._meta_dev.numel()), dtype=torch.int32,
-                                         device=self.device)
-        host = self._meta_host[turn].numpy()
+        host = self._meta.stage(lay.total)
         n_new_a, pos0_a = np.asarray(n_new, dtype=np.int64), np.asarray(pos0, dtype=np.int64)
         seq_start = np.zeros(B + 1, dtype=np.int64)
         np.cumsum(n_new_a, out=seq_start[1:])
@@ -184,17 +316,7 @@ class Engine:
         host[lay.want_rows:lay.want_rows + R] = want_rows
         for g in range(G):
             host[lay.tables[g]:lay.tables[g] + B * P] = self.cache.page_rows(g, slots).reshape(-1)
-        dev = self._meta_dev
-        dev[:lay.total].copy_(self._meta_host[turn][:lay.total], non_blocking=True)
-        event = torch.cuda.Event()
-        event.record()
-        self._meta_events[turn] = event
-        return StepContext(
-            n_tokens=N, n_seqs=B, n_want=R, is_decode=bool(n_new_a.max() == 1), max_new=int(n_new_a.max()),
-            max_context=int((pos0_a + n_new_a).max()), max_positions=self.max_seq_len, dtype=self.dtype, device=self.device, scratch=self.scratch,
-            token_ids=dev[lay.token_ids:lay.token_ids + N], token_seq=dev[lay.token_seq:lay.token_seq + N],
-            token_pos=dev[lay.token_pos:lay.token_pos + N], seq_slots=dev[lay.seq_slots:lay.seq_slots + B],
-            seq_start=dev[lay.seq_start:lay.seq_start + B + 1], seq_pos0=dev[lay.seq_pos0:lay.seq_pos0 + B],
-            want_rows=dev[lay.want_rows:lay.want_rows + max(R, 1)],
-            page_tables=[dev[lay.tables[g]:lay.tables[g] + B * P].view(B, P) for g in range(G)],
-            host_slots=list(slots), host_n_new=list(n_new), host_pos0=list(pos0))
+        self._meta.upload(lay.total)
+        self.last_upload_bytes = self._meta.bytes_last_upload
+        return self._context_views(self._meta.dev, lay, N, B, R, self.scratch, bool(n_new_a.max() == 1),
+                                   int(n_new_a.max()), int((pos0_a + n_new_a).max()), host=(slots, n_new, pos0))
