@@ -1,0 +1,163 @@
+// Weight-streaming matrix product for decode: Y[M,N] = X[M,K] . W[N,K]^T with a handful of
+// rows M (one per sequence of the batch), bfloat16 operands, 32-bit accumulation.
+//
+// In the reference every projection is one cublasGemmEx call whatever M is
+// (src/ops/linear.cpp:165-193).  With M <= 64 the product is bound by reading W once, so
+// this kernel is built around that stream: a block owns 16*R rows of W and splits K over
+// its warps; every lane reads 16 contiguous bytes of a W row per step and feeds them
+// straight to the tensor cores as the 16-row operand of mma.m16n8k16, with the batch rows
+// as the 8-column operand.  Since a sum over k does not care about the order of k, the
+// eight k-values a lane loads are used as they come (both operands permute k the same
+// way), so there is no shuffle and no shared-memory staging.  The warps' partial sums are
+// added in shared memory in warp order, which fixes the summation order for every M.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename OutT> __device__ __forceinline__ OutT to_out(float v);
+template <> __device__ __forceinline__ float to_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 to_out<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// MT: tiles of 8 batch rows (M <= 8*MT).  R: tiles of 16 rows of W per block.  WARPS: K is split over them.
+template <int MT, int R, int WARPS, typename OutT>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT* __restrict__ Y, int M, int N, int K) {
+    extern __shared__ __align__(16) float red[];   // [WARPS][8*MT][16*R + 1]
+    constexpr int ROWS = 16 * R, COLS = 8 * MT, LD = ROWS + 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane >> 2, tq = lane & 3;
+    const int n0 = blockIdx.x * ROWS;
+    const int nkb = (K + 31) >> 5;
+    const int kb_begin = (int)(((int64_t)warp * nkb) / WARPS), kb_end = (int)(((int64_t)(warp + 1) * nkb) / WARPS);
+
+    float acc[R][MT][4];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[r][m][0] = acc[r][m][1] = acc[r][m][2] = acc[r][m][3] = 0.0f;
+
+    const bf16* wrow[R][2];
+    bool wok[R][2];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int n = n0 + r * 16 + h * 8 + quad;
+            wok[r][h] = n < N;
+            wrow[r][h] = W + (int64_t)(wok[r][h] ? n : 0) * K + tq * 8;
+        }
+    const bf16* xrow[MT];
+    bool xok[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        const int row = m * 8 + quad;
+        xok[m] = row < M;
+        xrow[m] = X + (int64_t)(xok[m] ? row : 0) * K + tq * 8;
+    }
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+#pragma unroll 4
+    for (int kb = kb_begin; kb < kb_end; ++kb) {
+        const int k = kb * 32;
+        const bool kin = k + tq * 8 + 8 <= K;    // K is a multiple of 8: a chunk is inside or outside
+        uint4 w[R][2], x[MT];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) w[r][h] = (kin && wok[r][h]) ? ld_stream16(wrow[r][h] + k) : zero;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) x[m] = (kin && xok[m]) ? *reinterpret_cast<const uint4*>(xrow[m] + k) : zero;
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                mma_bf16(acc[r][m], w[r][0].x, w[r][1].x, w[r][0].y, w[r][1].y, x[m].x, x[m].y);
+                mma_bf16(acc[r][m], w[r][0].z, w[r][1].z, w[r][0].w, w[r][1].w, x[m].z, x[m].w);
+            }
+    }
+
+    // accumulator (row n = quad [+8], column m = 2*tq [+1]) -> red[warp][m][n]
+    float* mine = red + warp * COLS * LD;
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const int n = r * 16 + quad, c = m * 8 + tq * 2;
+            mine[c * LD + n] = acc[r][m][0];
+            mine[(c + 1) * LD + n] = acc[r][m][1];
+            mine[c * LD + n + 8] = acc[r][m][2];
+            mine[(c + 1) * LD + n + 8] = acc[r][m][3];
+        }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < ROWS * COLS; idx += WARPS * 32) {
+        const int n = idx % ROWS, m = idx / ROWS;
+        if (m >= M || n0 + n >= N) continue;
+        float sum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) sum += red[w * COLS * LD + m * LD + n];
+        Y[(int64_t)m * N + n0 + n] = to_out<OutT>(sum);
+    }
+}
+
+template <int MT, int R, int WARPS, typename OutT>
+int launch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, cudaStream_t stream) {
+    constexpr int SMEM = WARPS * 8 * MT * (16 * R + 1) * 4;
+    static bool configured = false;
+    if (SMEM > 48 * 1024 && !configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, R, WARPS, OutT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int blocks = (N + 16 * R - 1) / (16 * R);
+    gemm_skinny_kernel<MT, R, WARPS, OutT><<<blocks, WARPS * 32, SMEM, stream>>>(X, W, Y, M, N, K);
+    return (int)cudaGetLastError();
+}
+
+template <typename OutT>
+int dispatch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || M > 64) return Q3_ERR_BAD_SIZE;
+    if (!aligned16(X) || !aligned16(W)) return Q3_ERR_MISALIGNED;
+    // rows of W per block: as many as still leave about two blocks per SM
+    const int r = N >= 16 * 4 * 296 ? 4 : (N >= 16 * 2 * 296 ? 2 : 1);
+    const bool wide = N < 16 * 296 && K >= 2048;   // few blocks: more warps per block share K
+    if (M <= 8) {
+        if (r == 4) return launch<1, 4, 8, OutT>(X, W, Y, M, N, K, stream);
+        if (r == 2) return launch<1, 2, 8, OutT>(X, W, Y, M, N, K, stream);
+        return wide ? launch<1, 1, 16, OutT>(X, W, Y, M, N, K, stream) : launch<1, 1, 8, OutT>(X, W, Y, M, N, K, stream);
+    }
+    if (M <= 16) {
+        if (r == 4) return launch<2, 4, 8, OutT>(X, W, Y, M, N, K, stream);
+        if (r == 2) return launch<2, 2, 8, OutT>(X, W, Y, M, N, K, stream);
+        return wide ? launch<2, 1, 16, OutT>(X, W, Y, M, N, K, stream) : launch<2, 1, 8, OutT>(X, W, Y, M, N, K, stream);
+    }
+    if (M <= 32) {
+        if (r >= 2) return launch<4, 2, 8, OutT>(X, W, Y, M, N, K, stream);
+        return wide ? launch<4, 1, 16, OutT>(X, W, Y, M, N, K, stream) : launch<4, 1, 8, OutT>(X, W, Y, M, N, K, stream);
+    }
+    return wide ? launch<8, 1, 16, OutT>(X, W, Y, M, N, K, stream) : launch<8, 1, 8, OutT>(X, W, Y, M, N, K, stream);
+}
+
+}  // namespace
+
+Q3_EXPORT int q3_gemm_skinny_bf16(const void* X, const void* W, void* Y, int M, int N, int K, void* stream) {
+    return dispatch<bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, (cudaStream_t)stream);
+}
+
+Q3_EXPORT int q3_gemm_skinny_bf16_f32out(const void* X, const void* W, void* Y, int M, int N, int K, void* stream) {
+    return dispatch<float>((const bf16*)X, (const bf16*)W, (float*)Y, M, N, K, (cudaStream_t)stream);
+}

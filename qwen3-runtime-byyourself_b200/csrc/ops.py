@@ -45,6 +45,12 @@ def launch_count() -> int:
     return _launches
 
 
+def _count_extra(n: int) -> None:
+    """Entry points that launch more than one kernel add the rest here."""
+    global _launches
+    _launches += n
+
+
 def _check(code: int, name: str):
     global _launches
     _launches += 1
@@ -205,4 +211,55 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float, top_k: i
     _check(fn(_dev(logits, "logits", torch.float32), vocab, rows, int(valid or vocab), float(temperature), int(top_k),
               float(top_p), int(seed) & 0xFFFFFFFFFFFFFFFF, _dev(seq_ids, "seq_ids", torch.int64),
               _dev(steps, "steps", torch.int32), _dev(out, "out", torch.int32), _stream()), "sample")
+    return out
+
+
+# ------------------------------------------------------------------ bfloat16 decode attention
+def attention_decode_splits(n_tokens: int, nkv: int, sm_count: int = 148) -> int:
+    """Key splits so that the grid fills the GPU about twice; fixed by the batch size alone."""
+    return max(1, min(32, -(-2 * sm_count // max(1, n_tokens * nkv))))
+
+
+def attention_decode(q, k_pages, v_pages, out, scratch, token_seq, token_pos, page_table, n_tokens: int, nq: int,
+                     nkv: int, d: int, scale: float, window: Optional[int], n_splits: int):
+    """One token per sequence against its cached keys; `scratch` is float32 with at least
+    n_tokens * nq * n_splits * (d + 2) elements."""
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_decode is a bfloat16 kernel")
+    if nq // nkv > 16 or d % 16 != 0 or d > 256:
+        raise KernelError(f"attention_decode: group of {nq // nkv} heads or head_dim {d} not supported")
+    if scratch.numel() < n_tokens * nq * n_splits * (d + 2):
+        raise KernelError("attention_decode: scratch too small")
+    fn = _fn("attention_decode.cu", "q3_attention_decode_bf16",
+             [c_void_p] * 8 + [c_int, c_int64, c_int, c_int, c_float, c_int, c_int, c_void_p],
+             defines=(f"Q3_HEAD_DIM={d}",))
+    _check(fn(_dev(q, "q"), _dev(k_pages, "k_pages", torch.bfloat16), _dev(v_pages, "v_pages", torch.bfloat16),
+              _dev(out, "out", torch.bfloat16), _dev(scratch, "scratch", torch.float32),
+              _dev(token_seq, "token_seq", torch.int32), _dev(token_pos, "token_pos", torch.int32),
+              _dev(page_table, "page_table", torch.int32), page_table.shape[-1], n_tokens, nq, nkv, float(scale),
+              int(window or 0), int(n_splits), _stream()), "attention_decode")
+    _count_extra(1)
+    return out
+
+
+# ------------------------------------------------------------------ bfloat16 weight-streaming product
+SKINNY_MAX_ROWS = 64
+
+
+def gemm_skinny_fits(M: int, K: int) -> bool:
+    return 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T for M <= 64, bfloat16 operands, out bfloat16 or float32."""
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N) or not gemm_skinny_fits(M, K):
+        raise KernelError(f"gemm_skinny: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    name = {torch.bfloat16: "q3_gemm_skinny_bf16", torch.float32: "q3_gemm_skinny_bf16_f32out"}.get(out.dtype)
+    if name is None:
+        raise KernelError("gemm_skinny: output must be bfloat16 or float32")
+    fn = _fn("gemm_skinny_bf16.cu", name, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), M, N, K, _stream()),
+           "gemm_skinny")
     return out

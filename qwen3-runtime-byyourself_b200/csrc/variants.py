@@ -8,4 +8,6 @@ def all_variants():
         ("gemm_f32.cu", ()),
         ("attention.cu", ()),
         ("sampling.cu", ()),
+        ("attention_decode.cu", ("Q3_HEAD_DIM=128",)),
+        ("gemm_skinny_bf16.cu", ()),
     ]

@@ -14,6 +14,8 @@ table (src/model/model.cpp:81-88).
 """
 from __future__ import annotations
 
+import gc
+import weakref
 from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
@@ -116,7 +118,7 @@ class _DecodeGraph:
     belongs to no sequence; their logits are computed and dropped, no live row reads them."""
 
     def __init__(self, engine: "Engine", rows: int):
-        self.engine, self.rows = engine, rows
+        self.engine, self.rows = weakref.proxy(engine), rows      # no cycle: an engine dies with its last reference
         cache = engine.cache
         G, P = len(cache.groups), cache.pages_per_slot
         self.layout = _MetaLayout(rows, rows, rows, G, P)
@@ -160,8 +162,16 @@ class _DecodeGraph:
             torch.cuda.synchronize(self.engine.device)
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
-            with torch.cuda.graph(graph):
-                self.logits = model.forward(self.ctx, cache)
+            # an object that owns CUDA resources must not be collected in the middle of a capture
+            gc.collect()
+            gc_was_enabled = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                    self.logits = model.forward(self.ctx, cache)
+            finally:
+                if gc_was_enabled:
+                    gc.enable()
             self.launches = ops.launch_count() - before
             self.graph = graph
         self.graph.replay()

@@ -114,4 +114,18 @@ class GQAAttention(Part):
                         table, N, nq, nkv, d, 0.0)
 
 
+def _decode_split_kernel(part, q, cache, out, ctx, table) -> bool:
+    """The split-key tensor-core decode kernel: bfloat16, groups of up to 16 query heads."""
+    nq, nkv, d = part.num_heads, part.num_kv_heads, part.head_dim
+    if nq // nkv > 16:
+        return False
+    splits = ops.attention_decode_splits(ctx.n_tokens, nkv)
+    scratch = ctx.scratch.get("attn.decode_scratch", (ctx.n_tokens * nq * splits * (d + 2),), torch.float32)
+    ops.attention_decode(q, cache.keys, cache.values, out, scratch, ctx.token_seq, ctx.token_pos, table, ctx.n_tokens,
+                         nq, nkv, d, part.scale, part.window, splits)
+    return True
+
+
+DECODE_KERNELS.append(_decode_split_kernel)
+
 register_part("mixer", "gqa_attention", GQAAttention)

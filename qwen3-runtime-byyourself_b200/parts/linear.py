@@ -3,8 +3,9 @@
 32-bit operands go to the library's own fmaf kernel (true 32-bit, fixed summation
 order).  bfloat16 operands go to the cuBLAS product that torch wraps, as the
 reference's engine does for every projection (src/ops/linear.cpp:165-193:
-cublasGemmEx, bfloat16 in, 32-bit accumulate), unless a hand-written kernel is
-registered for the shape (`set_bf16_kernel`).
+cublasGemmEx, bfloat16 in, 32-bit accumulate), except for the few rows of a decode
+step, which run on the library's weight-streaming kernel, and unless another
+hand-written kernel is registered for the shape (`set_bf16_kernel`).
 """
 from __future__ import annotations
 
@@ -15,6 +16,7 @@ import torch
 from ..csrc import ops
 
 _bf16_kernel: Optional[Callable] = None
+skinny_rows = 16     # up to this many rows the weight-streaming kernel runs instead of the library
 
 
 def set_bf16_kernel(fn: Optional[Callable]) -> None:
@@ -35,6 +37,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         raise ops.KernelError("linear: CUDA tensors only")
     if _bf16_kernel is not None and _bf16_kernel(x, w, out):
         return out
+    if x.shape[0] <= skinny_rows and ops.gemm_skinny_fits(x.shape[0], x.shape[1]):
+        return ops.gemm_skinny(x, w, out)
     if out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     else:

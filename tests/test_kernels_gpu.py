@@ -297,3 +297,71 @@ def test_sampling_statistics_match_the_distribution():
     w = np.exp(np.array([2.0, 2.0, 1.5]) / 0.8)
     expect = w / w.sum() * n
     assert np.all(np.abs(counts[[0, 1, 7]] - expect) < 5 * np.sqrt(expect))
+
+
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (3, 301, 80), (8, 130, 1024), (9, 96, 288), (16, 4100, 512),
+                                   (17, 50, 4096), (33, 77, 160), (64, 1030, 2048), (5, 9600, 96), (12, 20000, 64)])
+def test_skinny_product(M, N, K, out_dtype):
+    """The weight-streaming kernel against float64, for every batch-row tile count, row-tile
+    count and K tail, and with rows that do not depend on the rest of the batch."""
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(M + N + K)
+    xd, wd = dev(rng.normal(0, 1, (M, K)), "bfloat16"), dev(rng.normal(0, 1, (N, K)), "bfloat16")
+    out = torch.empty(M, N, dtype=DT[out_dtype], device="cuda")
+    ops.gemm_skinny(xd, wd, out)
+    exact = back(xd) @ back(wd).T
+    if out_dtype == "float32":
+        assert np.max(np.abs(back(out) - exact)) <= 2e-5 * math.sqrt(K) * 4
+    else:
+        np.testing.assert_allclose(back(out), exact, atol=1e-2 * math.sqrt(K) / 8, rtol=8e-3)
+    one = torch.empty(1, N, dtype=DT[out_dtype], device="cuda")
+    ops.gemm_skinny(xd[M - 1:M].contiguous(), wd, one)
+    assert torch.equal(one[0], out[M - 1])
+
+
+@pytest.mark.parametrize("nq,nkv,d", [(4, 2, 16), (8, 1, 32), (6, 3, 48), (32, 8, 128), (16, 1, 64), (2, 2, 256), (5, 5, 80)])
+def test_decode_attention_split_kernel(nq, nkv, d):
+    """One new token per sequence against caches of very different lengths, for several split
+    counts, over shuffled pages: equal to float64 attention over the stored bfloat16 values."""
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(nq + d)
+    lengths = [1, 63, 64, 65, 130, 700, 1000]
+    table, kp, vp = paged_case(rng, lengths, nkv, d, "bfloat16")
+    table_d = torch.as_tensor(table).cuda()
+    keys = [rng.normal(0, 1, (n, nkv, d)) for n in lengths]
+    vals = [rng.normal(0, 1, (n, nkv, d)) for n in lengths]
+    for s, n in enumerate(lengths):
+        pages = table[s, :-(-n // 64)]
+        kpad = np.zeros((len(pages) * 64, nkv, d)); kpad[:n] = keys[s]
+        vpad = np.zeros((len(pages) * 64, nkv, d)); vpad[:n] = vals[s]
+        kp[torch.as_tensor(pages).long().cuda()] = dev(kpad.reshape(len(pages), 64, nkv, d).transpose(0, 2, 1, 3), "bfloat16")
+        vp[torch.as_tensor(pages).long().cuda()] = dev(vpad.reshape(len(pages), 64, nkv, d).transpose(0, 2, 1, 3), "bfloat16")
+    B = len(lengths)
+    q = rng.normal(0, 1, (B, nq, d))
+    q[5] *= 3.0
+    qd = dev(q.reshape(B, nq * d), "bfloat16")
+    seq = torch.arange(B, dtype=torch.int32, device="cuda")
+    pos = torch.as_tensor([n - 1 for n in lengths], dtype=torch.int32).cuda()
+    want = np.zeros((B, nq * d))
+    for s, n in enumerate(lengths):
+        qs = np.zeros((n, nq, d))
+        qs[n - 1] = back(qd)[s].reshape(nq, d)
+        want[s] = plain.gqa_attention(qs, stored(keys[s], "bfloat16"), stored(vals[s], "bfloat16"))[n - 1].reshape(-1)
+    for splits in (1, 2, 5, 32):
+        out = torch.zeros(B, nq * d, dtype=torch.bfloat16, device="cuda")
+        scratch = torch.full((B * nq * splits * (d + 2),), float("nan"), dtype=torch.float32, device="cuda")
+        ops.attention_decode(qd, kp, vp, out, scratch, seq, pos, table_d, B, nq, nkv, d, d ** -0.5, None, splits)
+        err = np.max(np.abs(back(out) - want))
+        assert err <= 1.5e-2, f"splits {splits}: max abs err {err:.3e}"
+    # the generic kernel agrees on the same cache
+    out2 = torch.zeros_like(out)
+    ops.attention_generic(qd, kp, vp, out2, seq, pos, table_d, B, nq, nkv, d, d ** -0.5)
+    assert np.max(np.abs(back(out2) - want)) <= 1.5e-2
+    # a window of 100 keys
+    out3 = torch.zeros_like(out)
+    scratch = torch.zeros(B * nq * 3 * (d + 2), dtype=torch.float32, device="cuda")
+    ops.attention_decode(qd, kp, vp, out3, scratch, seq, pos, table_d, B, nq, nkv, d, d ** -0.5, 100, 3)
+    ops.attention_generic(qd, kp, vp, out2, seq, pos, table_d, B, nq, nkv, d, d ** -0.5, 100)
+    assert np.max(np.abs(back(out3) - back(out2))) <= 1.5e-2
+    assert np.max(np.abs(back(out3)[6] - want[6])) > 1e-3      # the window really hides the older keys
