@@ -263,3 +263,22 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Te
     _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), M, N, K, _stream()),
            "gemm_skinny")
     return out
+
+
+# ------------------------------------------------------------------ bfloat16 prompt attention
+def attention_prefill(q, k_pages, v_pages, out, seq_start, seq_pos0, page_table, n_seqs: int, max_new: int, nq: int,
+                      nkv: int, d: int, scale: float, window: Optional[int] = None):
+    """Causal attention of every new token of every sequence over its pages (tiled, tensor cores)."""
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill is a bfloat16 kernel")
+    if d % 16 != 0 or d > 256:
+        raise KernelError(f"head_dim {d} is not supported: multiples of 16 up to 256")
+    fn = _fn("attention_prefill.cu", "q3_attention_prefill_bf16",
+             [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+             defines=(f"Q3_HEAD_DIM={d}",))
+    _check(fn(_dev(q, "q"), _dev(k_pages, "k_pages", torch.bfloat16), _dev(v_pages, "v_pages", torch.bfloat16),
+              _dev(out, "out", torch.bfloat16), _dev(seq_start, "seq_start", torch.int32),
+              _dev(seq_pos0, "seq_pos0", torch.int32), _dev(page_table, "page_table", torch.int32),
+              page_table.shape[-1], n_seqs, max_new, nq, nkv, float(scale), int(window or 0), _stream()),
+           "attention_prefill")
+    return out

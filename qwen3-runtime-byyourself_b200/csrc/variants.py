@@ -10,4 +10,5 @@ def all_variants():
         ("sampling.cu", ()),
         ("attention_decode.cu", ("Q3_HEAD_DIM=128",)),
         ("gemm_skinny_bf16.cu", ()),
+        ("attention_prefill.cu", ("Q3_HEAD_DIM=128",)),
     ]

@@ -126,6 +126,14 @@ def _decode_split_kernel(part, q, cache, out, ctx, table) -> bool:
     return True
 
 
+def _prefill_flash_kernel(part, q, cache, out, ctx, table) -> bool:
+    """The tiled tensor-core kernel for steps that bring prompts (or any mix of lengths)."""
+    ops.attention_prefill(q, cache.keys, cache.values, out, ctx.seq_start, ctx.seq_pos0, table, ctx.n_seqs,
+                          ctx.max_new, part.num_heads, part.num_kv_heads, part.head_dim, part.scale, part.window)
+    return True
+
+
 DECODE_KERNELS.append(_decode_split_kernel)
+PREFILL_KERNELS.append(_prefill_flash_kernel)
 
 register_part("mixer", "gqa_attention", GQAAttention)

@@ -365,3 +365,44 @@ def test_decode_attention_split_kernel(nq, nkv, d):
     ops.attention_generic(qd, kp, vp, out2, seq, pos, table_d, B, nq, nkv, d, d ** -0.5, 100)
     assert np.max(np.abs(back(out3) - back(out2))) <= 1.5e-2
     assert np.max(np.abs(back(out3)[6] - want[6])) > 1e-3      # the window really hides the older keys
+
+
+@pytest.mark.parametrize("nq,nkv,d", [(4, 2, 16), (8, 1, 32), (6, 3, 48), (8, 2, 128), (2, 2, 256), (5, 5, 80)])
+@pytest.mark.parametrize("window", [None, 90])
+def test_prefill_attention_tiled_kernel(nq, nkv, d, window):
+    """Prompts of unequal length in one launch, then a second launch that continues them from the
+    cache (positions > 0, tiles that straddle page edges), against float64 causal attention."""
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(nq * 31 + d)
+    lengths, first = [200, 5, 129, 64, 333], [64, 1, 100, 63, 130]
+    table, kp, vp = paged_case(rng, lengths, nkv, d, "bfloat16")
+    table_d = torch.as_tensor(table).cuda()
+    full = [rng.normal(0, 1, (n, (nq + 2 * nkv) * d)) for n in lengths]
+    got = [np.zeros((n, nq * d)) for n in lengths]
+    for part in range(2):
+        spans = [(0, f) if part == 0 else (f, n) for f, n in zip(first, lengths)]
+        rows = np.concatenate([full[s][a:b] for s, (a, b) in enumerate(spans)])
+        seq = np.concatenate([np.full(b - a, s) for s, (a, b) in enumerate(spans)]).astype(np.int32)
+        pos = np.concatenate([np.arange(a, b) for a, b in spans]).astype(np.int32)
+        starts = np.cumsum([0] + [b - a for a, b in spans]).astype(np.int32)
+        N = rows.shape[0]
+        q = torch.empty(N, nq * d, dtype=torch.bfloat16, device="cuda")
+        out = torch.zeros_like(q)
+        seq_d, pos_d = torch.as_tensor(seq).cuda(), torch.as_tensor(pos).cuda()
+        ops.qkv_prepare(dev(rows, "bfloat16"), q, kp, vp, None, None, None, None, seq_d, pos_d, table_d, N, nq, nkv, d, 0.0)
+        ops.attention_prefill(q, kp, vp, out, torch.as_tensor(starts).cuda(),
+                              torch.as_tensor([a for a, _ in spans], dtype=torch.int32).cuda(), table_d, len(lengths),
+                              max(b - a for a, b in spans), nq, nkv, d, d ** -0.5, window)
+        o = back(out)
+        k = 0
+        for s, (a, b) in enumerate(spans):
+            got[s][a:b] = o[k:k + b - a]
+            k += b - a
+    for s, n in enumerate(lengths):
+        x = stored(full[s], "bfloat16")
+        qs = x[:, :nq * d].reshape(n, nq, d)
+        ks = x[:, nq * d:(nq + nkv) * d].reshape(n, nkv, d)
+        vs = x[:, (nq + nkv) * d:].reshape(n, nkv, d)
+        want = plain.gqa_attention(qs, ks, vs, window=window).reshape(n, nq * d)
+        err = np.abs(got[s] - want).max(axis=1)
+        assert err.max() <= 2e-2, f"sequence {s}: row {int(err.argmax())} of {n}: max abs err {err.max():.3e}"
