@@ -30,6 +30,8 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_
                                    const float* __restrict__ sin_tab, const int* __restrict__ token_seq,
                                    const int* __restrict__ token_pos, const int* __restrict__ page_table,
                                    int pages_per_seq, int nq, int nkv, int d, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.x * warps + warp;
     if (head >= nq + 2 * nkv) return;
@@ -103,6 +105,8 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
     __shared__ float q_s[MAX_HEAD_DIM];
     __shared__ float score[PAGE];
     __shared__ float prob[PAGE];
+    pdl_launch_dependents();
+    pdl_wait();
     const int head = blockIdx.x, kvh = head / (nq / nkv);
     const int64_t t = blockIdx.y;
     const int pos = token_pos[t];
@@ -161,10 +165,8 @@ int qkv_prepare_launch(const T* qkv, T* q_out, T* k_pages, T* v_pages, const flo
     if (n_tokens > 65535) return Q3_ERR_TOO_LARGE;
     const int warps = 4;
     const dim3 grid((nq + 2 * nkv + warps - 1) / warps, (unsigned)n_tokens);
-    qkv_prepare_kernel<T><<<grid, warps * 32, 0, stream>>>(qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, cos_tab,
-                                                            sin_tab, token_seq, token_pos, page_table, pages_per_seq,
-                                                            nq, nkv, d, eps);
-    return (int)cudaGetLastError();
+    return (int)q3_launch(qkv_prepare_kernel<T>, grid, dim3(warps * 32), 0, stream, qkv, q_out, k_pages, v_pages, q_norm_w,
+                          k_norm_w, cos_tab, sin_tab, token_seq, token_pos, page_table, pages_per_seq, nq, nkv, d, eps);
 }
 
 template <typename T>
@@ -175,9 +177,8 @@ int attention_generic_launch(const T* q, const T* k_pages, const T* v_pages, T* 
     if (d <= 0 || d > MAX_HEAD_DIM || nq <= 0 || nkv <= 0 || nq % nkv != 0) return Q3_ERR_BAD_SIZE;
     if (n_tokens > 65535) return Q3_ERR_TOO_LARGE;
     const dim3 grid(nq, (unsigned)n_tokens);
-    attention_generic_kernel<T><<<grid, 128, 0, stream>>>(q, k_pages, v_pages, out, token_seq, token_pos, page_table,
-                                                           pages_per_seq, nq, nkv, d, scale, window);
-    return (int)cudaGetLastError();
+    return (int)q3_launch(attention_generic_kernel<T>, grid, dim3(128), 0, stream, q, k_pages, v_pages, out, token_seq,
+                          token_pos, page_table, pages_per_seq, nq, nkv, d, scale, window);
 }
 
 }  // namespace

@@ -79,6 +79,8 @@ decode_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                     const int* __restrict__ token_pos, const int* __restrict__ page_table, int pages_per_seq, int nq,
                     int nkv, float scale_log2, int window) {
     extern __shared__ __align__(16) unsigned char smem[];
+    pdl_launch_dependents();
+    pdl_wait();
     const int split = blockIdx.x, n_splits = gridDim.x, kvh = blockIdx.y, t = blockIdx.z;
     const int G = nq / nkv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -244,6 +246,8 @@ decode_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
 // One block per (head, token): out = sum_s w_s o_s / sum_s w_s l_s with w_s = 2^(m_s - max m).
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int nq, int n_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t row = (int64_t)blockIdx.y * nq + blockIdx.x;
     const float* ml = part_ml + row * n_splits * 2;
     float m = -INFINITY;
@@ -286,12 +290,10 @@ Q3_EXPORT int q3_attention_decode_bf16(const void* q, const void* k_pages, const
     float* part_o = scratch;
     float* part_ml = scratch + n_tokens * nq * n_splits * D;
     const dim3 grid(n_splits, nkv, (unsigned)n_tokens);
-    decode_split_kernel<<<grid, WARPS * 32, SMEM_BYTES, stream>>>(
-        (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, part_o, part_ml, token_seq, token_pos, page_table,
-        pages_per_seq, nq, nkv, scale * 1.4426950408889634f, window);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = q3_launch(decode_split_kernel, grid, dim3(WARPS * 32), SMEM_BYTES, stream, (const bf16*)q,
+                              (const bf16*)k_pages, (const bf16*)v_pages, part_o, part_ml, token_seq, token_pos, page_table,
+                              pages_per_seq, nq, nkv, scale * 1.4426950408889634f, window);
     if (e != cudaSuccess) return (int)e;
-    decode_merge_kernel<<<dim3(nq, (unsigned)n_tokens), D < 128 ? 32 : 128, 0, stream>>>(part_o, part_ml, (bf16*)out, nq,
-                                                                                       n_splits);
-    return (int)cudaGetLastError();
+    return (int)q3_launch(decode_merge_kernel, dim3(nq, (unsigned)n_tokens), dim3(D < 128 ? 32 : 128), 0, stream,
+                          (const float*)part_o, (const float*)part_ml, (bf16*)out, nq, n_splits);
 }

@@ -71,6 +71,8 @@ prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, con
                bf16* __restrict__ out, const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
                const int* __restrict__ page_table, int pages_per_seq, int nq, int nkv, float scale_log2, int window) {
     extern __shared__ __align__(16) unsigned char smem[];
+    pdl_launch_dependents();
+    pdl_wait();
     const int tile = blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
     const int t0 = seq_start[seq], n_new = seq_start[seq + 1] - t0;
     if (tile * BM >= n_new) return;
@@ -232,8 +234,7 @@ Q3_EXPORT int q3_attention_prefill_bf16(const void* q, const void* k_pages, cons
         configured = true;
     }
     const dim3 grid((max_new + BM - 1) / BM, nq, n_seqs);
-    prefill_kernel<<<grid, WARPS * 32, SMEM_BYTES, (cudaStream_t)stream>>>(
-        (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, seq_start, seq_pos0, page_table,
-        pages_per_seq, nq, nkv, scale * 1.4426950408889634f, window);
-    return (int)cudaGetLastError();
+    return (int)q3_launch(prefill_kernel, grid, dim3(WARPS * 32), SMEM_BYTES, (cudaStream_t)stream, (const bf16*)q,
+                          (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, seq_start, seq_pos0, page_table,
+                          pages_per_seq, nq, nkv, scale * 1.4426950408889634f, window);
 }

@@ -17,6 +17,37 @@ typedef __nv_bfloat16 bf16;
 #define Q3_ERR_TOO_LARGE 10002
 #define Q3_ERR_MISALIGNED 10003
 
+// ---- programmatic dependent launch ------------------------------------------------------
+// Kernels of a step run back to back on one stream.  Launched with the programmatic
+// attribute, a kernel may start while its predecessor drains: it does what needs no input
+// of the predecessor (address arithmetic, fetching weights) and then waits in `pdl_wait()`,
+// which returns once the predecessor has completed and its writes are visible.  Rules that
+// every kernel here keeps: `pdl_launch_dependents()` first thing, and no read of an
+// activation and no write to global memory before `pdl_wait()`.  Without the attribute
+// both calls do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static int g_q3_pdl = 0;
+// Switches the programmatic attribute on or off for the launches of this library.
+Q3_EXPORT void q3_set_pdl(int on) { g_q3_pdl = on; }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t q3_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_q3_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }

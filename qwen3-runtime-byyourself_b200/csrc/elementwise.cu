@@ -37,6 +37,8 @@ template <typename T, int VEC> __device__ __forceinline__ void store_vec(T* p, c
 template <typename T, int VEC>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
                                  int hidden, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < vocab;
@@ -62,10 +64,10 @@ static int embedding_launch(const int* ids, const T* table, T* out, int64_t n_to
     const bool vec = hidden % V == 0 && aligned16(table) && aligned16(out);
     const int threads = 128;
     if (vec)
-        embedding_kernel<T, V><<<(unsigned)n_tokens, threads, 0, stream>>>(ids, table, out, hidden, vocab);
-    else
-        embedding_kernel<T, 1><<<(unsigned)n_tokens, threads, 0, stream>>>(ids, table, out, hidden, vocab);
-    return (int)cudaGetLastError();
+        return (int)q3_launch(embedding_kernel<T, V>, dim3((unsigned)n_tokens), dim3(threads), 0, stream, ids, table, out,
+                              hidden, vocab);
+    return (int)q3_launch(embedding_kernel<T, 1>, dim3((unsigned)n_tokens), dim3(threads), 0, stream, ids, table, out,
+                          hidden, vocab);
 }
 
 // ---------------------------------------------------------------- RMSNorm (+ residual sum)
@@ -75,6 +77,8 @@ template <typename T, int VEC>
 __global__ void rms_norm_kernel(T* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ w,
                                 T* __restrict__ y, int size, float eps, int64_t x_stride, int64_t y_stride) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t row = blockIdx.x;
     T* xr = x + row * x_stride;
     const T* dr = delta ? delta + row * x_stride : nullptr;
@@ -116,16 +120,18 @@ static int rms_norm_launch(T* x, const T* delta, const float* w, T* y, int64_t r
     int threads = (size / per + 31) / 32 * 32;
     threads = threads < 32 ? 32 : (threads > 512 ? 512 : threads);
     if (vec)
-        rms_norm_kernel<T, V><<<(unsigned)rows, threads, 0, stream>>>(x, delta, w, y, size, eps, x_stride, y_stride);
-    else
-        rms_norm_kernel<T, 1><<<(unsigned)rows, threads, 0, stream>>>(x, delta, w, y, size, eps, x_stride, y_stride);
-    return (int)cudaGetLastError();
+        return (int)q3_launch(rms_norm_kernel<T, V>, dim3((unsigned)rows), dim3(threads), 0, stream, x, delta, w, y, size,
+                              eps, x_stride, y_stride);
+    return (int)q3_launch(rms_norm_kernel<T, 1>, dim3((unsigned)rows), dim3(threads), 0, stream, x, delta, w, y, size, eps,
+                          x_stride, y_stride);
 }
 
 // ---------------------------------------------------------------- SiLU(gate) * up
 // gate_up: [rows, 2*inter] with the gate in the first `inter` columns; out: [rows, inter].
 template <typename T, int VEC>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t rows, int inter) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t per_row = inter / VEC;
     const int64_t total = rows * per_row;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -151,10 +157,9 @@ static int silu_mul_launch(const T* gate_up, T* out, int64_t rows, int inter, cu
     int64_t blocks = (work + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (vec)
-        silu_mul_kernel<T, V><<<(unsigned)blocks, threads, 0, stream>>>(gate_up, out, rows, inter);
-    else
-        silu_mul_kernel<T, 1><<<(unsigned)blocks, threads, 0, stream>>>(gate_up, out, rows, inter);
-    return (int)cudaGetLastError();
+        return (int)q3_launch(silu_mul_kernel<T, V>, dim3((unsigned)blocks), dim3(threads), 0, stream, gate_up, out, rows,
+                              inter);
+    return (int)q3_launch(silu_mul_kernel<T, 1>, dim3((unsigned)blocks), dim3(threads), 0, stream, gate_up, out, rows, inter);
 }
 
 // ---------------------------------------------------------------- gather rows (+ pending branch)
@@ -163,6 +168,8 @@ static int silu_mul_launch(const T* gate_up, T* out, int64_t rows, int inter, cu
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, const T* __restrict__ delta, const int* __restrict__ idx,
                                    T* __restrict__ out, int size) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t r = blockIdx.x;
     const int64_t src = idx[r];
     for (int c = threadIdx.x; c < size; c += blockDim.x) {
@@ -176,8 +183,7 @@ template <typename T>
 static int gather_rows_launch(const T* x, const T* delta, const int* idx, T* out, int64_t rows, int size,
                               cudaStream_t stream) {
     if (rows <= 0) return 0;
-    gather_rows_kernel<T><<<(unsigned)rows, 256, 0, stream>>>(x, delta, idx, out, size);
-    return (int)cudaGetLastError();
+    return (int)q3_launch(gather_rows_kernel<T>, dim3((unsigned)rows), dim3(256), 0, stream, x, delta, idx, out, size);
 }
 
 // ---------------------------------------------------------------- exported entry points

@@ -18,6 +18,8 @@ gemm_tn_f32_kernel(const float* __restrict__ X, const float* __restrict__ W, flo
                    int64_t ldx, int64_t ldw, int64_t ldy) {
     __shared__ float Xs[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int tx = tid % 16, ty = tid / 16;  // thread tile: rows ty*4.., cols tx*4..
@@ -94,8 +96,8 @@ Q3_EXPORT int q3_gemm_tn_f32(const float* X, const float* W, float* Y, int M, in
     if (grid.y > 65535) return Q3_ERR_TOO_LARGE;
     const bool vec = aligned16(X) && aligned16(W) && ldx % 4 == 0 && ldw % 4 == 0;
     if (vec)
-        gemm_tn_f32_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(X, W, Y, M, N, K, ldx, ldw, ldy);
-    else
-        gemm_tn_f32_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(X, W, Y, M, N, K, ldx, ldw, ldy);
-    return (int)cudaGetLastError();
+        return (int)q3_launch(gemm_tn_f32_kernel<true>, grid, dim3(256), 0, (cudaStream_t)stream, X, W, Y, M, N, K, ldx, ldw,
+                              ldy);
+    return (int)q3_launch(gemm_tn_f32_kernel<false>, grid, dim3(256), 0, (cudaStream_t)stream, X, W, Y, M, N, K, ldx, ldw,
+                          ldy);
 }

@@ -8,36 +8,41 @@
 // straight to the tensor cores as the 16-row operand of mma.m16n8k16, with the batch rows
 // as the 8-column operand.  Since a sum over k does not care about the order of k, the
 // eight k-values a lane loads are used as they come (both operands permute k the same
-// way), so there is no shuffle and no shared-memory staging.  The warps' partial sums are
+// way), so there is no shuffle and no shared-memory staging.  Each warp keeps several
+// k-blocks of W in flight in registers, and the first of them are requested before the
+// kernel waits for its predecessor (weights do not depend on it), so the stream of W
+// starts while the kernel before this one drains.  The warps' partial sums are
 // added in shared memory in warp order, which fixes the summation order for every M.
 #include "common.cuh"
 
 namespace {
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    uint4 v;   // not volatile: the compiler may hoist and batch these loads
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 template <typename OutT> __device__ __forceinline__ OutT to_out(float v);
 template <> __device__ __forceinline__ float to_out<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 to_out<bf16>(float v) { return __float2bfloat16_rn(v); }
 
-// MT: tiles of 8 batch rows (M <= 8*MT).  R: tiles of 16 rows of W per block.  WARPS: K is split over them.
-template <int MT, int R, int WARPS, typename OutT>
+// MT: tiles of 8 batch rows (M <= 8*MT).  R: tiles of 16 rows of W per block.  WARPS: K is split
+// over them.  PF: k-blocks (of 32) a warp keeps in flight in registers.
+template <int MT, int R, int WARPS, int PF, typename OutT>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT* __restrict__ Y, int M, int N, int K) {
     extern __shared__ __align__(16) float red[];   // [WARPS][8*MT][16*R + 1]
     constexpr int ROWS = 16 * R, COLS = 8 * MT, LD = ROWS + 1;
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane >> 2, tq = lane & 3;
     const int n0 = blockIdx.x * ROWS;
     const int nkb = (K + 31) >> 5;
@@ -68,25 +73,43 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT*
         xrow[m] = X + (int64_t)(xok[m] ? row : 0) * K + tq * 8;
     }
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    uint4 w[PF][R][2], x[PF][MT];
 
-#pragma unroll 4
-    for (int kb = kb_begin; kb < kb_end; ++kb) {
+    auto load_w = [&](int s, int kb) {
         const int k = kb * 32;
-        const bool kin = k + tq * 8 + 8 <= K;    // K is a multiple of 8: a chunk is inside or outside
-        uint4 w[R][2], x[MT];
+        const bool in = kb < kb_end && k + tq * 8 + 8 <= K;   // K is a multiple of 8: a chunk is inside or outside
 #pragma unroll
         for (int r = 0; r < R; ++r)
 #pragma unroll
-            for (int h = 0; h < 2; ++h) w[r][h] = (kin && wok[r][h]) ? ld_stream16(wrow[r][h] + k) : zero;
+            for (int h = 0; h < 2; ++h) w[s][r][h] = (in && wok[r][h]) ? ld_stream16(wrow[r][h] + k) : zero;
+    };
+    auto load_x = [&](int s, int kb) {
+        const int k = kb * 32;
+        const bool in = kb < kb_end && k + tq * 8 + 8 <= K;
 #pragma unroll
-        for (int m = 0; m < MT; ++m) x[m] = (kin && xok[m]) ? *reinterpret_cast<const uint4*>(xrow[m] + k) : zero;
+        for (int m = 0; m < MT; ++m) x[s][m] = (in && xok[m]) ? *reinterpret_cast<const uint4*>(xrow[m] + k) : zero;
+    };
+
+    // the weights do not depend on the kernel before this one: fetch the first blocks, then wait for it
 #pragma unroll
-        for (int r = 0; r < R; ++r)
+    for (int s = 0; s < PF; ++s) load_w(s, kb_begin + s);
+    pdl_wait();
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                mma_bf16(acc[r][m], w[r][0].x, w[r][1].x, w[r][0].y, w[r][1].y, x[m].x, x[m].y);
-                mma_bf16(acc[r][m], w[r][0].z, w[r][1].z, w[r][0].w, w[r][1].w, x[m].z, x[m].w);
-            }
+    for (int s = 0; s < PF; ++s) load_x(s, kb_begin + s);
+
+    for (int kb = kb_begin; kb < kb_end; kb += PF) {
+#pragma unroll
+        for (int s = 0; s < PF; ++s) {
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    mma_bf16(acc[r][m], w[s][r][0].x, w[s][r][1].x, w[s][r][0].y, w[s][r][1].y, x[s][m].x, x[s][m].y);
+                    mma_bf16(acc[r][m], w[s][r][0].z, w[s][r][1].z, w[s][r][0].w, w[s][r][1].w, x[s][m].z, x[s][m].w);
+                }
+            load_w(s, kb + s + PF);      // blocks past the end load zeros, which add nothing
+            load_x(s, kb + s + PF);
+        }
     }
 
     // accumulator (row n = quad [+8], column m = 2*tq [+1]) -> red[warp][m][n]
@@ -107,7 +130,7 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT*
         if (m >= M || n0 + n >= N) continue;
         float sum = 0.0f;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) sum += red[w * COLS * LD + m * LD + n];
+        for (int w2 = 0; w2 < WARPS; ++w2) sum += red[w2 * COLS * LD + m * LD + n];
         Y[(int64_t)m * N + n0 + n] = to_out<OutT>(sum);
     }
 }
@@ -115,16 +138,17 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT*
 template <int MT, int R, int WARPS, typename OutT>
 int launch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, cudaStream_t stream) {
     constexpr int SMEM = WARPS * 8 * MT * (16 * R + 1) * 4;
+    constexpr int PF = (8 / (R * MT)) < 2 ? 2 : (8 / (R * MT));
     static bool configured = false;
     if (SMEM > 48 * 1024 && !configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, R, WARPS, OutT>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, R, WARPS, PF, OutT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const int blocks = (N + 16 * R - 1) / (16 * R);
-    gemm_skinny_kernel<MT, R, WARPS, OutT><<<blocks, WARPS * 32, SMEM, stream>>>(X, W, Y, M, N, K);
-    return (int)cudaGetLastError();
+    return (int)q3_launch(gemm_skinny_kernel<MT, R, WARPS, PF, OutT>, dim3(blocks), dim3(WARPS * 32), SMEM, stream, X, W,
+                          Y, M, N, K);
 }
 
 template <typename OutT>

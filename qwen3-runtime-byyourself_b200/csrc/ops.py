@@ -8,6 +8,7 @@ to a library: a CPU tensor or a missing compiler is an error.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_int64, c_uint64, c_void_p
 from typing import Optional
 
@@ -25,11 +26,31 @@ class KernelError(RuntimeError):
     """A kernel refused its arguments or its launch failed."""
 
 
+_pdl = os.environ.get("QWEN3_B200_PDL", "0") == "1"
+_libs = {}
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for every kernel of the library: a kernel may start (and
+    fetch weights) while the one before it on the stream drains.  Off by default (measured
+    slower for whole decode steps, where chains of waiting kernels take the SMs' room);
+    the environment variable QWEN3_B200_PDL=1 turns it on."""
+    global _pdl
+    _pdl = bool(on)
+    for lib in _libs.values():
+        lib.q3_set_pdl(int(_pdl))
+
+
 def _fn(source: str, name: str, argtypes, defines=()):
     key = (source, name, tuple(defines))
     fn = _fn_cache.get(key)
     if fn is None:
         lib = load_library(source, defines)
+        if (source, tuple(defines)) not in _libs:
+            _libs[(source, tuple(defines))] = lib
+            lib.q3_set_pdl.argtypes = [c_int]
+            lib.q3_set_pdl.restype = None
+            lib.q3_set_pdl(int(_pdl))
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int

@@ -52,6 +52,8 @@ __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, int64_t stride, int valid, int* __restrict__ out) {
     __shared__ float best_v[THREADS / 32];
     __shared__ int best_i[THREADS / 32];
+    pdl_launch_dependents();
+    pdl_wait();
     const float* x = logits + (int64_t)blockIdx.x * stride;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
@@ -138,6 +140,8 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int valid, float
     __shared__ unsigned long long total_s;
     __shared__ int counts[THREADS];
     __shared__ int found[2];
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
     const float* x = logits + (int64_t)row * stride;
 
@@ -239,8 +243,7 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int valid, float
 Q3_EXPORT int q3_argmax_f32(const float* logits, int64_t stride, int rows, int valid, int* out, void* stream) {
     if (rows <= 0) return 0;
     if (valid <= 0 || valid > stride) return Q3_ERR_BAD_SIZE;
-    argmax_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(logits, stride, valid, out);
-    return (int)cudaGetLastError();
+    return (int)q3_launch(argmax_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, logits, stride, valid, out);
 }
 
 // out[row] = -1 marks a row with a non-finite logit.
@@ -250,7 +253,6 @@ Q3_EXPORT int q3_sample_f32(const float* logits, int64_t stride, int rows, int v
     if (rows <= 0) return 0;
     if (valid <= 0 || valid > stride || !(temperature > 0.0f) || top_k < 0 || !(top_p > 0.0f && top_p <= 1.0f))
         return Q3_ERR_BAD_SIZE;
-    sample_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(logits, stride, valid, temperature, top_k, top_p, seed,
-                                                               seq_ids, steps, out);
-    return (int)cudaGetLastError();
+    return (int)q3_launch(sample_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, logits, stride, valid,
+                          temperature, top_k, top_p, seed, seq_ids, steps, out);
 }
