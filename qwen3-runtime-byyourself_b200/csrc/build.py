@@ -3,7 +3,7 @@
 Each `.cu` file becomes one shared library, compiled the first time one of its entry
 points is needed: a model only pays for the kernels it uses (an attention kernel is
 compiled for the model's own head size through `-D` definitions).  The library's name
-carries a hash of the source, the shared header, the definitions and the flags, so a
+carries a hash of the source, the files it includes, the definitions and the flags, so a
 stale build is never loaded.  Libraries are kept under `csrc/_build/` inside the
 package when that folder can be written, else under a per-user temporary folder; no
 home directory is needed.  There is no fallback: without nvcc, or when the compile
@@ -63,10 +63,27 @@ def build_dir() -> str:
     raise KernelBuildError(f"no writable build folder among {candidates}")
 
 
+def _sources_of(source: str):
+    """`source` and every file of this folder that it includes, directly or not."""
+    seen, todo = [], [source]
+    while todo:
+        name = todo.pop()
+        path = os.path.join(HERE, name)
+        if name in seen or not os.path.isfile(path):
+            continue
+        seen.append(name)
+        with open(path, "r", encoding="utf-8") as f:
+            for line in f:
+                line = line.strip()
+                if line.startswith("#include \""):
+                    todo.append(line.split("\"")[1])
+    return sorted(seen)
+
+
 def _digest(source: str, defines: Tuple[str, ...], extra: Tuple[str, ...]) -> str:
     h = hashlib.sha256()
-    for path in (os.path.join(HERE, source), os.path.join(HERE, "common.cuh")):
-        with open(path, "rb") as f:
+    for name in _sources_of(source):
+        with open(os.path.join(HERE, name), "rb") as f:
             h.update(f.read())
     h.update(repr((defines, extra, ARCH_FLAGS, BASE_FLAGS)).encode())
     return h.hexdigest()[:12]

@@ -11,4 +11,5 @@ def all_variants():
         ("attention_decode.cu", ("Q3_HEAD_DIM=128",)),
         ("gemm_skinny_bf16.cu", ()),
         ("attention_prefill.cu", ("Q3_HEAD_DIM=128",)),
+        ("attention_decode_static.cu", ("Q3_HEAD_DIM=128",)),
     ]
