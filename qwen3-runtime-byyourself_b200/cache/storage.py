@@ -3,12 +3,14 @@
 Layout of one group: [layer in group, K|V, page, kv head, token in page, head_dim].
 A (page, kv head) tile is one contiguous [PAGE_TOKENS, head_dim] panel, so a kernel
 streams whole panels and a 2-D bulk copy can fetch one.  State rows are float32
-[slot, *state_shape] per layer and are zeroed when the slot is handed out.  Every group
+[slot, *state_shape] per layer and are zeroed when the slot is handed out; row number
+`n_slots` belongs to no sequence and takes the padding rows of a fixed-size decode batch.  Every group
 has one page more than its pool hands out: page number `n_pages` belongs to no
 sequence and takes the writes of the padding rows of a fixed-size decode batch.
 """
 from __future__ import annotations
 
+import dataclasses
 from dataclasses import dataclass
 from typing import Dict, Optional, Sequence
 
@@ -25,6 +27,7 @@ class LayerCache:
     values: Optional[torch.Tensor]
     state: Optional[torch.Tensor]     # [n_slots, *state_shape] float32
     window: Optional[int] = None
+    shared: bool = False              # the view of a layer that reads another layer's cache: it must not write
 
 
 class KVCache(CacheBook):
@@ -36,7 +39,7 @@ class KVCache(CacheBook):
             torch.zeros((len(g.layers), 2, g.n_pages + 1, g.need.num_kv_heads, PAGE_TOKENS, g.need.head_dim),
                         dtype=dtype, device=self.device)
             for g in self.groups]
-        self.states = {layer: torch.zeros((self.n_slots,) + shape, dtype=torch.float32, device=self.device)
+        self.states = {layer: torch.zeros((self.n_slots + 1,) + shape, dtype=torch.float32, device=self.device)
                        for layer, shape in self.state_layers.items()}
         self._views: Dict[int, LayerCache] = {}
         for layer, need in enumerate(needs):
@@ -50,7 +53,7 @@ class KVCache(CacheBook):
             self._views[layer] = LayerCache(gi, keys, values, self.states.get(layer),
                                             need.window if need.kind == "window" else None)
         for layer, src in (cache_from or {}).items():
-            self._views[layer] = self._views[src]
+            self._views[layer] = dataclasses.replace(self._views[src], shared=True)
 
     def _on_alloc(self, slot: int) -> None:
         for state in self.states.values():

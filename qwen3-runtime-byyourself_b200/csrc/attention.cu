@@ -29,12 +29,12 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_
                                    const float* __restrict__ k_norm_w, const float* __restrict__ cos_tab,
                                    const float* __restrict__ sin_tab, const int* __restrict__ token_seq,
                                    const int* __restrict__ token_pos, const int* __restrict__ page_table,
-                                   int pages_per_seq, int nq, int nkv, int d, float eps) {
+                                   int pages_per_seq, int nq, int nkv, int d, float eps, int write_kv) {
     pdl_launch_dependents();
     pdl_wait();
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.x * warps + warp;
-    if (head >= nq + 2 * nkv) return;
+    if (head >= nq + 2 * nkv || (head >= nq && !write_kv)) return;   // a layer that reads another layer's cache writes none
     const int64_t t = blockIdx.y;
     const int pos = token_pos[t];
     const int half = d >> 1;
@@ -159,14 +159,14 @@ template <typename T>
 int qkv_prepare_launch(const T* qkv, T* q_out, T* k_pages, T* v_pages, const float* q_norm_w, const float* k_norm_w,
                        const float* cos_tab, const float* sin_tab, const int* token_seq, const int* token_pos,
                        const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps,
-                       cudaStream_t stream) {
+                       int write_kv, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (d <= 0 || d % 2 != 0 || d > MAX_HEAD_DIM || nq <= 0 || nkv <= 0) return Q3_ERR_BAD_SIZE;
     if (n_tokens > 65535) return Q3_ERR_TOO_LARGE;
     const int warps = 4;
     const dim3 grid((nq + 2 * nkv + warps - 1) / warps, (unsigned)n_tokens);
     return (int)q3_launch(qkv_prepare_kernel<T>, grid, dim3(warps * 32), 0, stream, qkv, q_out, k_pages, v_pages, q_norm_w,
-                          k_norm_w, cos_tab, sin_tab, token_seq, token_pos, page_table, pages_per_seq, nq, nkv, d, eps);
+                          k_norm_w, cos_tab, sin_tab, token_seq, token_pos, page_table, pages_per_seq, nq, nkv, d, eps, write_kv);
 }
 
 template <typename T>
@@ -188,10 +188,10 @@ int attention_generic_launch(const T* q, const T* k_pages, const T* v_pages, T* 
                                           const float* q_norm_w, const float* k_norm_w, const float* cos_tab,         \
                                           const float* sin_tab, const int* token_seq, const int* token_pos,           \
                                           const int* page_table, int pages_per_seq, int64_t n_tokens, int nq,         \
-                                          int nkv, int d, float eps, void* stream) {                                  \
+                                          int nkv, int d, float eps, int write_kv, void* stream) {                   \
         return qkv_prepare_launch<T>((const T*)qkv, (T*)q_out, (T*)k_pages, (T*)v_pages, q_norm_w, k_norm_w, cos_tab, \
                                      sin_tab, token_seq, token_pos, page_table, pages_per_seq, n_tokens, nq, nkv, d,  \
-                                     eps, (cudaStream_t)stream);                                                      \
+                                     eps, write_kv, (cudaStream_t)stream);                                            \
     }                                                                                                                 \
     Q3_EXPORT int q3_attention_generic_##SUFFIX(const void* q, const void* k_pages, const void* v_pages, void* out,   \
                                                 const int* token_seq, const int* token_pos, const int* page_table,    \

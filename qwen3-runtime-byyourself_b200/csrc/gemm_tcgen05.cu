@@ -1,0 +1,317 @@
+// Blackwell matrix product for the projections: Y[M,N] = X[M,K] . W[N,K]^T, bfloat16
+// operands, 32-bit accumulation in tensor memory, bfloat16 or float32 output.
+//
+// It replaces the reference's cublasGemmEx call per projection (src/ops/linear.cpp:165-193).
+// The tile is computed "weights first": D[128 rows of W, BN tokens] = W_tile . X_tile^T, so
+// the 128-row operand of tcgen05.mma is always full whatever the number of tokens, and the
+// same kernel serves prompts (BN = 128 or 256 tokens per tile) and decode steps (BN = 16..64,
+// K split over blockIdx.z with float32 partial tiles).
+//
+// One tile per block; three roles:
+//   warp 0     TMA producer: cp.async.bulk.tensor loads of the W and X tiles (128-byte
+//              swizzle, K-major) into a ring of shared-memory stages, signalled by mbarriers
+//   warp 1     allocates tensor memory; one thread issues tcgen05.mma (M=128, N=BN, K=16,
+//              four per stage) and commits each stage back to the producer
+//   warps 2-5  epilogue: tcgen05.ld of the accumulator (one TMEM lane = one row of W per
+//              thread), conversion, and stores Y[token][row] that are contiguous over a warp
+// Every wait on an mbarrier is bounded: after Q3_WAIT_LIMIT polls the thread records where it
+// gave up in `status` and the block winds down (tensor memory is freed on every path).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;                 // rows of W per tile (the UMMA M)
+constexpr int BK = 64;                  // K per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr uint32_t Q3_WAIT_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait: true if the phase completed, false if the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < Q3_WAIT_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, groups of
+// eight rows 1024 bytes apart.  Bits: [0,14) address>>4, [16,30) leading offset>>4 (unused for
+// swizzled K-major, 1), [32,46) stride offset>>4, [46,48) version 1, [61,64) layout 2 (128B).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+// Instruction descriptor of kind::f16: float32 accumulator, bfloat16 A and B, both K-major.
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <typename OutT> __device__ __forceinline__ OutT to_out(float v);
+template <> __device__ __forceinline__ float to_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 to_out<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+template <int BN, int STAGES> struct Smem {
+    static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;          // both multiples of 1024
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+// Y is [splits, M, N] when gridDim.z > 1 (float32 partial sums), else [M, N].
+template <int BN, int STAGES, typename OutT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    OutT* __restrict__ Y, int M, int N, int K, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    using S = Smem<BN, STAGES>;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;         // 128-byte swizzle wants 1024-byte tiles
+    const uint32_t bars = base + STAGES * S::STAGE_BYTES;                 // full[STAGES], empty[STAGES], done, tmem slot
+    const uint32_t bar_done = bars + 2 * STAGES * 8, tmem_slot = bar_done + 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN;
+    const int nkb_all = (K + BK - 1) / BK;
+    const int kb_begin = (int)(((int64_t)blockIdx.z * nkb_all) / gridDim.z);
+    const int kb_end = (int)(((int64_t)(blockIdx.z + 1) * nkb_all) / gridDim.z);
+    const int nkb = kb_end - kb_begin;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bars + s * 8, 1);
+            mbar_init(bars + (STAGES + s) * 8, 1);
+        }
+        mbar_init(bar_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+    if (warp == 0) {
+        // ---------------- producer
+        if (lane == 0) {
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
+                ok = mbar_wait(bars + (STAGES + s) * 8, phase ^ 1u);         // the stage is free
+                if (!ok) { atomicExch(status, 1); break; }
+                const uint32_t a = base + s * S::STAGE_BYTES, b = a + S::A_BYTES;
+                mbar_expect_tx(bars + s * 8, S::STAGE_BYTES);
+                tma_load_2d(a, &map_w, bars + s * 8, (kb_begin + i) * BK, n0);      // weights: independent of the
+                if (i == 0) pdl_wait();                                              // kernel before; X is not
+                tma_load_2d(b, &map_x, bars + s * 8, (kb_begin + i) * BK, m0);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BN);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
+                ok = mbar_wait(bars + s * 8, phase);                         // the tiles have landed
+                if (!ok) { atomicExch(status, 2); break; }
+                tc_fence_after();
+                const uint32_t a = base + s * S::STAGE_BYTES, b = a + S::A_BYTES;
+                const uint64_t da = make_desc(a), db = make_desc(b);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)                        // 32 bytes further along K per step
+                    tc_mma(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                tc_commit(bars + (STAGES + s) * 8);                          // frees the stage when the MMAs are done
+            }
+            tc_commit(bar_done);                                             // accumulator complete (or abandoned)
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 own TMEM lanes 32*(warp % 4) ..
+        const bool ok = mbar_wait(bar_done, 0);
+        if (!ok && lane == 0) atomicExch(status, 3);
+        tc_fence_after();
+        pdl_wait();                                                          // no global write before this
+        if (ok && nkb > 0) {
+            const int lane_base = (warp & 3) * 32;
+            const int n = n0 + lane_base + lane;
+            OutT* y = Y + (int64_t)blockIdx.z * M * N;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t r[16];
+                tc_ld16(tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)c, r);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int m = m0 + c + j;
+                    if (m < M && n < N) y[(int64_t)m * N + n] = to_out<OutT>(__uint_as_float(r[j]));
+                }
+            }
+        } else if (ok) {                                                      // an empty K range adds nothing
+            const int n = n0 + (warp & 3) * 32 + lane;
+            OutT* y = Y + (int64_t)blockIdx.z * M * N;
+            for (int j = 0; j < BN; ++j)
+                if (m0 + j < M && n < N) y[(int64_t)(m0 + j) * N + n] = to_out<OutT>(0.0f);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// out[m, n] = sum over splits of part[s, m, n], in split order.
+template <typename OutT>
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, OutT* __restrict__ out, int64_t count, int splits) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
+        float sum = 0.0f;
+        for (int s = 0; s < splits; ++s) sum += part[s * count + i];
+        out[i] = to_out<OutT>(sum);
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// A [rows, K] bfloat16 row-major matrix, fetched in boxes of [box_rows, 64] with 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+    EncodeTiled fn = encode_fn();
+    if (fn == nullptr) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, typename OutT>
+int launch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int splits, int* status, cudaStream_t stream) {
+    using S = Smem<BN, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, OutT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    CUtensorMap map_w, map_x;
+    if (!make_map(&map_w, W, N, K, BM) || !make_map(&map_x, X, M, K, BN)) return Q3_ERR_BAD_SIZE;
+    const dim3 grid((N + BM - 1) / BM, (M + BN - 1) / BN, splits);
+    return (int)q3_launch(gemm_tcgen05_kernel<BN, STAGES, OutT>, grid, dim3(THREADS), (size_t)S::TOTAL, stream, map_w, map_x,
+                          Y, M, N, K, status);
+}
+
+}  // namespace
+
+// Direct product (one K range per tile).  `tile_n` picks the token tile: 16, 32, 64, 128 or 256.
+// `status` is a device int that a kernel sets to 1/2/3 if a bounded wait ran out (0 otherwise).
+Q3_EXPORT int q3_gemm_tcgen05_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int tile_n,
+                                   int* status, void* stream_) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0) return Q3_ERR_BAD_SIZE;
+    if (!aligned16(X) || !aligned16(W)) return Q3_ERR_MISALIGNED;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const bf16* x = (const bf16*)X;
+    const bf16* w = (const bf16*)W;
+#define Q3_TC_CASE(BN, ST)                                                                               \
+    if (tile_n == BN)                                                                                    \
+        return out_is_f32 ? launch<BN, ST, float>(x, w, (float*)Y, M, N, K, 1, status, stream)           \
+                          : launch<BN, ST, bf16>(x, w, (bf16*)Y, M, N, K, 1, status, stream);
+    Q3_TC_CASE(16, 8)
+    Q3_TC_CASE(32, 8)
+    Q3_TC_CASE(64, 8)
+    Q3_TC_CASE(128, 6)
+    Q3_TC_CASE(256, 4)
+#undef Q3_TC_CASE
+    return Q3_ERR_BAD_SIZE;
+}
+
+// Split-K product for a handful of rows: partial tiles go to `scratch` (float32 [splits, M, N]) and
+// are summed in split order.
+Q3_EXPORT int q3_gemm_tcgen05_splitk_bf16(const void* X, const void* W, void* Y, float* scratch, int M, int N, int K,
+                                          int out_is_f32, int tile_n, int splits, int* status, void* stream_) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || splits <= 0) return Q3_ERR_BAD_SIZE;
+    if (!aligned16(X) || !aligned16(W)) return Q3_ERR_MISALIGNED;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const bf16* x = (const bf16*)X;
+    const bf16* w = (const bf16*)W;
+    int rc = Q3_ERR_BAD_SIZE;
+    if (tile_n == 16) rc = launch<16, 8, float>(x, w, scratch, M, N, K, splits, status, stream);
+    if (tile_n == 32) rc = launch<32, 8, float>(x, w, scratch, M, N, K, splits, status, stream);
+    if (tile_n == 64) rc = launch<64, 8, float>(x, w, scratch, M, N, K, splits, status, stream);
+    if (rc != 0) return rc;
+    const int64_t count = (int64_t)M * N;
+    const int blocks = (int)((count + 255) / 256 < 1184 ? (count + 255) / 256 : 1184);
+    if (out_is_f32)
+        return (int)q3_launch(splitk_reduce_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)scratch,
+                              (float*)Y, count, splits);
+    return (int)q3_launch(splitk_reduce_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const float*)scratch, (bf16*)Y,
+                          count, splits);
+}

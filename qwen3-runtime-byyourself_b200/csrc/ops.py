@@ -179,21 +179,22 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tenso
 
 # ------------------------------------------------------------------ attention
 def qkv_prepare(qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, cos, sin, token_seq, token_pos, page_table,
-                n_tokens: int, nq: int, nkv: int, d: int, eps: float):
-    """Per-head norm of q and k, rotation, and the write of k and v into the cache pages."""
+                n_tokens: int, nq: int, nkv: int, d: int, eps: float, write_kv: bool = True):
+    """Per-head norm of q and k, rotation, and the write of k and v into the cache pages
+    (`write_kv=False`: only q is prepared, for a layer that reads another layer's cache)."""
     s = _suffix(qkv)
     if d % 16 != 0 or d > 256:
         raise KernelError(f"head_dim {d} is not supported: multiples of 16 up to 256")
     if qkv.shape[-1] != (nq + 2 * nkv) * d or k_pages.dtype != qkv.dtype or k_pages.shape[1:] != (nkv, 64, d):
         raise KernelError("qkv_prepare: shapes do not fit")
     fn = _fn("attention.cu", f"q3_qkv_prepare_{s}",
-             [c_void_p] * 11 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_void_p])
+             [c_void_p] * 11 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_void_p])
     _check(fn(_dev(qkv, "qkv"), _dev(q_out, "q_out", qkv.dtype), _dev(k_pages, "k_pages"), _dev(v_pages, "v_pages"),
               _ptr(q_norm_w, "q_norm_w", torch.float32), _ptr(k_norm_w, "k_norm_w", torch.float32),
               _ptr(cos, "cos", torch.float32), _ptr(sin, "sin", torch.float32),
               _dev(token_seq, "token_seq", torch.int32), _dev(token_pos, "token_pos", torch.int32),
               _dev(page_table, "page_table", torch.int32), page_table.shape[-1], n_tokens, nq, nkv, d, float(eps),
-              _stream()), "qkv_prepare")
+              int(bool(write_kv)), _stream()), "qkv_prepare")
     return q_out
 
 
@@ -302,4 +303,70 @@ def attention_prefill(q, k_pages, v_pages, out, seq_start, seq_pos0, page_table,
               _dev(seq_pos0, "seq_pos0", torch.int32), _dev(page_table, "page_table", torch.int32),
               page_table.shape[-1], n_seqs, max_new, nq, nkv, float(scale), int(window or 0), _stream()),
            "attention_prefill")
+    return out
+
+
+# ------------------------------------------------------------------ bfloat16 tcgen05 product
+_tc_status = {}
+
+
+def _status_word(device) -> torch.Tensor:
+    word = _tc_status.get(device)
+    if word is None:
+        word = _tc_status[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return word
+
+
+def tcgen05_status(device) -> int:
+    """0, or where a bounded wait inside the tcgen05 product gave up (1 producer, 2 MMA, 3 epilogue);
+    reading it synchronises the device and clears it."""
+    word = _status_word(torch.device(device))
+    value = int(word.item())
+    if value:
+        word.zero_()
+    return value
+
+
+def tcgen05_tile(M: int) -> int:
+    """The token tile for M rows: the smallest of 16..256 that covers M, 256 beyond."""
+    for t in (16, 32, 64, 128):
+        if M <= t:
+            return t
+    return 256 if M > 512 else 128
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_n: Optional[int] = None) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T on the 5th-generation tensor cores (TMA-fed, accumulator in
+    tensor memory); bfloat16 operands, out bfloat16 or float32; K a multiple of 8."""
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N) or K % 8 != 0:
+        raise KernelError(f"gemm_tcgen05: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_tcgen05: output must be bfloat16 or float32")
+    fn = _fn("gemm_tcgen05.cu", "q3_gemm_tcgen05_bf16",
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), M, N, K,
+              int(out.dtype == torch.float32), int(tile_n or tcgen05_tile(M)), _status_word(x.device).data_ptr(),
+              _stream()), "gemm_tcgen05")
+    return out
+
+
+def gemm_tcgen05_splitk(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, splits: int,
+                        tile_n: Optional[int] = None) -> torch.Tensor:
+    """The same product for at most 64 rows with K split over `splits` blocks; `scratch` is float32
+    with at least splits * M * N elements."""
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N) or K % 8 != 0 or M > 64:
+        raise KernelError(f"gemm_tcgen05_splitk: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    if scratch.numel() < splits * M * N:
+        raise KernelError("gemm_tcgen05_splitk: scratch too small")
+    fn = _fn("gemm_tcgen05.cu", "q3_gemm_tcgen05_splitk_bf16",
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"),
+              _dev(scratch, "scratch", torch.float32), M, N, K, int(out.dtype == torch.float32),
+              int(tile_n or tcgen05_tile(M)), int(splits), _status_word(x.device).data_ptr(), _stream()),
+           "gemm_tcgen05_splitk")
+    _count_extra(1)
     return out

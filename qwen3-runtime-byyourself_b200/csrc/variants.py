@@ -12,4 +12,5 @@ def all_variants():
         ("gemm_skinny_bf16.cu", ()),
         ("attention_prefill.cu", ("Q3_HEAD_DIM=128",)),
         ("attention_decode_static.cu", ("Q3_HEAD_DIM=128",)),
+        ("gemm_tcgen05.cu", ()),
     ]

@@ -102,6 +102,50 @@ class _MetaBuffer:
         self.bytes_last_upload = total * 4
 
 
+def context_views(cache, dev, lay, N, B, R, scratch, dtype, max_positions, is_decode, max_new, max_context,
+                  host=None) -> StepContext:
+    """A StepContext whose device fields are views of the metadata buffer `dev` laid out by `lay`."""
+    G, P = len(cache.groups), cache.pages_per_slot
+    return StepContext(
+        n_tokens=N, n_seqs=B, n_want=R, is_decode=is_decode, max_new=max_new, max_context=max_context,
+        max_positions=max_positions, dtype=dtype, device=dev.device, scratch=scratch,
+        token_ids=dev[lay.token_ids:lay.token_ids + N], token_seq=dev[lay.token_seq:lay.token_seq + N],
+        token_pos=dev[lay.token_pos:lay.token_pos + N], seq_slots=dev[lay.seq_slots:lay.seq_slots + B],
+        seq_start=dev[lay.seq_start:lay.seq_start + B + 1], seq_pos0=dev[lay.seq_pos0:lay.seq_pos0 + B],
+        want_rows=dev[lay.want_rows:lay.want_rows + max(R, 1)],
+        page_tables=[dev[lay.tables[g]:lay.tables[g] + B * P].view(B, P) for g in range(G)],
+        host_slots=list(host[0]) if host else [], host_n_new=list(host[1]) if host else [],
+        host_pos0=list(host[2]) if host else [])
+
+
+def build_context(cache, meta: "_MetaBuffer", scratch, dtype, max_positions, slots, n_new, pos0, token_ids,
+                  want_rows) -> StepContext:
+    """Pack one step's metadata, upload it with one copy and return the context the parts read.
+    `cache.reserve` must have made room for the step already (the page rows are read here)."""
+    token_ids = np.asarray(token_ids, dtype=np.int64).reshape(-1)
+    B, N, R = len(slots), int(token_ids.size), len(want_rows)
+    G, P = len(cache.groups), cache.pages_per_slot
+    lay = _MetaLayout(N, B, R, G, P)
+    host = meta.stage(lay.total)
+    n_new_a, pos0_a = np.asarray(n_new, dtype=np.int64), np.asarray(pos0, dtype=np.int64)
+    seq_start = np.zeros(B + 1, dtype=np.int64)
+    np.cumsum(n_new_a, out=seq_start[1:])
+    token_seq = np.repeat(np.arange(B, dtype=np.int64), n_new_a)
+    token_pos = np.arange(N, dtype=np.int64) - seq_start[:-1][token_seq] + pos0_a[token_seq]
+    host[lay.token_ids:lay.token_ids + N] = token_ids
+    host[lay.token_seq:lay.token_seq + N] = token_seq
+    host[lay.token_pos:lay.token_pos + N] = token_pos
+    host[lay.seq_slots:lay.seq_slots + B] = slots
+    host[lay.seq_start:lay.seq_start + B + 1] = seq_start
+    host[lay.seq_pos0:lay.seq_pos0 + B] = pos0_a
+    host[lay.want_rows:lay.want_rows + R] = want_rows
+    for g in range(G):
+        host[lay.tables[g]:lay.tables[g] + B * P] = cache.page_rows(g, slots).reshape(-1)
+    meta.upload(lay.total)
+    return context_views(cache, meta.dev, lay, N, B, R, scratch, dtype, max_positions, bool(n_new_a.max() == 1),
+                         int(n_new_a.max()), int((pos0_a + n_new_a).max()), host=(slots, n_new, pos0))
+
+
 def decode_bucket(n: int) -> int:
     """Fixed batch sizes for captured decode steps: 1..8 exactly, then multiples of 8, of 32 above 64."""
     if n <= 8:
@@ -125,8 +169,8 @@ class _DecodeGraph:
         self.meta = _MetaBuffer(engine.device)
         self.meta.reserve(self.layout.total)
         self.scratch = Scratch(engine.device)
-        self.ctx = engine._context_views(self.meta.dev, self.layout, rows, rows, rows, self.scratch, is_decode=True,
-                                         max_new=1, max_context=engine.max_seq_len)
+        self.ctx = context_views(cache, self.meta.dev, self.layout, rows, rows, rows, self.scratch, engine.dtype,
+                                 engine.max_seq_len, is_decode=True, max_new=1, max_context=engine.max_seq_len)
         self.graph = None
         self.logits = None
         self.launches = 0
@@ -139,6 +183,7 @@ class _DecodeGraph:
         host[lay.token_ids:lay.token_ids + B] = token_ids
         host[lay.token_seq:lay.token_seq + rows] = np.arange(rows)
         host[lay.token_pos:lay.token_pos + B] = pos0
+        host[lay.seq_slots:lay.seq_slots + rows] = cache.n_slots      # the spare state row for padding
         host[lay.seq_slots:lay.seq_slots + B] = slots
         host[lay.seq_start:lay.seq_start + rows + 1] = np.arange(rows + 1)
         host[lay.seq_pos0:lay.seq_pos0 + B] = pos0
@@ -150,30 +195,36 @@ class _DecodeGraph:
             table[:B] = cache.page_rows(g, slots)
         self.meta.upload(lay.total)
 
+    def _capture(self) -> None:
+        """Warm up and capture on a batch of padding rows only: whatever a mixer writes while the
+        step is recorded (cache pages, state rows) lands in the spare page and the spare row."""
+        from ..csrc import ops
+        model, cache = self.engine.model, self.engine.cache
+        self._fill([], [], [])
+        model.forward(self.ctx, cache)               # loads kernels and library handles outside the capture
+        torch.cuda.synchronize(self.engine.device)
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        # an object that owns CUDA resources must not be collected in the middle of a capture
+        gc.collect()
+        gc_was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                self.logits = model.forward(self.ctx, cache)
+        finally:
+            if gc_was_enabled:
+                gc.enable()
+        self.launches = ops.launch_count() - before
+        self.graph = graph
+
     def run(self, slots, pos0, token_ids, device_tokens=None) -> torch.Tensor:
         """Logits [rows, vocab] of the captured step; rows beyond len(slots) are padding."""
+        if self.graph is None:
+            self._capture()
         self._fill(slots, pos0, token_ids)
         if device_tokens is not None:
             self.ctx.token_ids[:len(slots)].copy_(device_tokens)
-        if self.graph is None:
-            from ..csrc import ops
-            model, cache = self.engine.model, self.engine.cache
-            model.forward(self.ctx, cache)           # loads kernels and library handles outside the capture
-            torch.cuda.synchronize(self.engine.device)
-            graph = torch.cuda.CUDAGraph()
-            before = ops.launch_count()
-            # an object that owns CUDA resources must not be collected in the middle of a capture
-            gc.collect()
-            gc_was_enabled = gc.isenabled()
-            gc.disable()
-            try:
-                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                    self.logits = model.forward(self.ctx, cache)
-            finally:
-                if gc_was_enabled:
-                    gc.enable()
-            self.launches = ops.launch_count() - before
-            self.graph = graph
         self.graph.replay()
         self.engine.launches += self.launches
         return self.logits
@@ -197,7 +248,8 @@ class Engine:
         self.vocab_size = self.plan.vocab_size
         self.scratch = Scratch(self.device)
         self._meta = _MetaBuffer(self.device)
-        self.use_graphs = use_graphs
+        # a mixer whose step depends on host values (not only on the context's device fields) opts out
+        self.use_graphs = use_graphs and all(getattr(b.mixer, "graph_safe", True) for b in model.blocks)
         self._graphs = {}
         self.launches = 0          # kernels of this library launched by steps (replayed graph nodes included)
         self.last_upload_bytes = 0
@@ -294,39 +346,8 @@ class Engine:
             return logits[:len(want_rows)]
         return logits[torch.as_tensor(want_rows, device=self.device)]
 
-    def _context_views(self, dev, lay, N, B, R, scratch, is_decode, max_new, max_context, host=None) -> StepContext:
-        G, P = len(self.cache.groups), self.cache.pages_per_slot
-        return StepContext(
-            n_tokens=N, n_seqs=B, n_want=R, is_decode=is_decode, max_new=max_new, max_context=max_context,
-            max_positions=self.max_seq_len, dtype=self.dtype, device=self.device, scratch=scratch,
-            token_ids=dev[lay.token_ids:lay.token_ids + N], token_seq=dev[lay.token_seq:lay.token_seq + N],
-            token_pos=dev[lay.token_pos:lay.token_pos + N], seq_slots=dev[lay.seq_slots:lay.seq_slots + B],
-            seq_start=dev[lay.seq_start:lay.seq_start + B + 1], seq_pos0=dev[lay.seq_pos0:lay.seq_pos0 + B],
-            want_rows=dev[lay.want_rows:lay.want_rows + max(R, 1)],
-            page_tables=[dev[lay.tables[g]:lay.tables[g] + B * P].view(B, P) for g in range(G)],
-            host_slots=list(host[0]) if host else [], host_n_new=list(host[1]) if host else [],
-            host_pos0=list(host[2]) if host else [])
-
     def _build_context(self, slots, n_new, pos0, token_ids, want_rows) -> StepContext:
-        B, N, R = len(slots), int(token_ids.size), len(want_rows)
-        G, P = len(self.cache.groups), self.cache.pages_per_slot
-        lay = _MetaLayout(N, B, R, G, P)
-        host = self._meta.stage(lay.total)
-        n_new_a, pos0_a = np.asarray(n_new, dtype=np.int64), np.asarray(pos0, dtype=np.int64)
-        seq_start = np.zeros(B + 1, dtype=np.int64)
-        np.cumsum(n_new_a, out=seq_start[1:])
-        token_seq = np.repeat(np.arange(B, dtype=np.int64), n_new_a)
-        token_pos = np.arange(N, dtype=np.int64) - seq_start[:-1][token_seq] + pos0_a[token_seq]
-        host[lay.token_ids:lay.token_ids + N] = token_ids
-        host[lay.token_seq:lay.token_seq + N] = token_seq
-        host[lay.token_pos:lay.token_pos + N] = token_pos
-        host[lay.seq_slots:lay.seq_slots + B] = slots
-        host[lay.seq_start:lay.seq_start + B + 1] = seq_start
-        host[lay.seq_pos0:lay.seq_pos0 + B] = pos0_a
-        host[lay.want_rows:lay.want_rows + R] = want_rows
-        for g in range(G):
-            host[lay.tables[g]:lay.tables[g] + B * P] = self.cache.page_rows(g, slots).reshape(-1)
-        self._meta.upload(lay.total)
+        ctx = build_context(self.cache, self._meta, self.scratch, self.dtype, self.max_seq_len, slots, n_new, pos0,
+                            token_ids, want_rows)
         self.last_upload_bytes = self._meta.bytes_last_upload
-        return self._context_views(self._meta.dev, lay, N, B, R, self.scratch, bool(n_new_a.max() == 1),
-                                   int(n_new_a.max()), int((pos0_a + n_new_a).max()), host=(slots, n_new, pos0))
+        return ctx

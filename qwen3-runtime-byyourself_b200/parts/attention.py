@@ -82,7 +82,7 @@ class GQAAttention(Part):
                 self.position.prepare(ctx.max_positions, ctx.device)
                 cos, sin = self.position.cos, self.position.sin
             ops.qkv_prepare(qkv, q, cache.keys, cache.values, qw, kw, cos, sin, ctx.token_seq, ctx.token_pos, table,
-                            N, nq, nkv, d, norm_eps)
+                            N, nq, nkv, d, norm_eps, write_kv=not cache.shared)
         else:
             self._prepare_unfused(qkv, q, cache, ctx, table, qw, kw, norm_eps)
         attn = ctx.scratch.get("attn.ctx", (N, nq * d), ctx.dtype)
@@ -111,7 +111,7 @@ class GQAAttention(Part):
         self.position.apply_(qs, ks, ctx.token_pos[:N])
         packed = torch.cat([qs.view(N, -1), ks.view(N, -1), qkv[:, (nq + nkv) * d:]], dim=1).contiguous()
         ops.qkv_prepare(packed, q, cache.keys, cache.values, None, None, None, None, ctx.token_seq, ctx.token_pos,
-                        table, N, nq, nkv, d, 0.0)
+                        table, N, nq, nkv, d, 0.0, write_kv=not cache.shared)
 
 
 def _decode_split_kernel(part, q, cache, out, ctx, table) -> bool:

@@ -43,8 +43,9 @@ class RotaryEmbedding(Part):
         s = self.sin[positions.long()][:, None, :]
         for t in (q, k):
             a, b = t[..., :half].float(), t[..., half:].float()
-            t[..., :half] = (a * c - b * s).to(t.dtype)
-            t[..., half:] = (b * c + a * s).to(t.dtype)
+            first, second = a * c - b * s, b * c + a * s     # both from the unrotated values
+            t[..., :half] = first.to(t.dtype)
+            t[..., half:] = second.to(t.dtype)
 
 
 register_part("position", "rope", RotaryEmbedding)

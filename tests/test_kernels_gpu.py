@@ -406,3 +406,42 @@ def test_prefill_attention_tiled_kernel(nq, nkv, d, window):
         want = plain.gqa_attention(qs, ks, vs, window=window).reshape(n, nq * d)
         err = np.abs(got[s] - want).max(axis=1)
         assert err.max() <= 2e-2, f"sequence {s}: row {int(err.argmax())} of {n}: max abs err {err.max():.3e}"
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 128, 64), (1, 128, 64), (5, 256, 128), (17, 200, 80), (64, 384, 512),
+                                   (100, 301, 96), (128, 128, 4096), (300, 1000, 1024), (2048, 512, 640)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+def test_tcgen05_product(M, N, K, out_dtype):
+    """The TMA + tcgen05 kernel against a 32-bit product of the same bfloat16 operands, for
+    every token tile, ragged edges in all three dimensions, and K that is no multiple of 64."""
+    from qwen3_b200.csrc import ops
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N + K)
+    x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g, device="cuda").to(torch.bfloat16)
+    want = (x.double() @ w.double().T)
+    tiles = sorted({ops.tcgen05_tile(M)} | ({16, 64} if M <= 16 else set()) | ({256} if M > 128 else set()))
+    for tile in tiles:
+        out = torch.full((M, N), float("nan"), dtype=DT[out_dtype], device="cuda")
+        ops.gemm_tcgen05(x, w, out, tile_n=tile)
+        assert ops.tcgen05_status("cuda") == 0, f"a wait inside the kernel gave up (tile {tile})"
+        err = (out.double() - want).abs().max().item()
+        bound = 4e-5 * math.sqrt(K) * 4 if out_dtype == "float32" else 0.02 * math.sqrt(K)
+        assert err <= bound, f"tile {tile}: max abs err {err:.3e} > {bound:.3e}"
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(8, 4096, 4096, 4), (1, 256, 512, 8), (16, 384, 12288, 6), (33, 200, 1000, 3),
+                                          (64, 128, 64, 4)])
+def test_tcgen05_split_k_product(M, N, K, splits):
+    from qwen3_b200.csrc import ops
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g, device="cuda").to(torch.bfloat16)
+    want = (x.double() @ w.double().T)
+    for out_dtype in ("bfloat16", "float32"):
+        out = torch.full((M, N), float("nan"), dtype=DT[out_dtype], device="cuda")
+        scratch = torch.full((splits * M * N,), float("nan"), dtype=torch.float32, device="cuda")
+        ops.gemm_tcgen05_splitk(x, w, out, scratch, splits)
+        assert ops.tcgen05_status("cuda") == 0
+        err = (out.double() - want).abs().max().item()
+        bound = 4e-5 * math.sqrt(K) * 4 if out_dtype == "float32" else 0.02 * math.sqrt(K)
+        assert err <= bound, f"max abs err {err:.3e} > {bound:.3e}"

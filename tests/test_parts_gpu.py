@@ -1,0 +1,230 @@
+"""Each part alone against its plain formula, and a toy mixer with state of its own that is
+defined here, registered, built into a model from a plan and stepped through the engine
+without any change to the library's files."""
+import dataclasses
+
+import numpy as np
+import pytest
+
+from helpers import make_folder, tiny
+from plain import qwen3_plain as plain
+import schedules
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def context_for(cache, slots, n_new, token_ids, dtype, want=()):
+    """Reserve and build a step context outside any engine (what `Engine.step` does first)."""
+    from qwen3_b200.engine.context import Scratch
+    from qwen3_b200.engine.engine import _MetaBuffer, build_context
+    step = list(zip(slots, n_new))
+    cache.reserve(step)
+    pos0 = [cache.length(s) for s in slots]
+    ctx = build_context(cache, _MetaBuffer(cache.device), Scratch(cache.device), dtype, cache.max_seq_len, slots, n_new,
+                        pos0, token_ids, list(want))
+    return ctx, step
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_position_and_feed_forward_parts(dtype):
+    import qwen3_b200 as q
+    from qwen3_b200.cache.storage import KVCache
+    from qwen3_b200.parts import build_part
+    rng = np.random.default_rng(0)
+    rnd = plain.identity if dtype == torch.float32 else plain.round_bf16
+    tol = 3e-5 if dtype == torch.float32 else 3e-2
+    # norm
+    norm = build_part("norm", q.PartSpec("rms_norm", {"size": 72, "eps": 2e-4}))
+    w = torch.tensor(1 + rng.normal(0, 0.1, 72), dtype=torch.bfloat16)
+    norm.bind({"n.weight": w}, "n.weight", dtype, "cuda")
+    x = torch.tensor(rng.normal(0, 3, (5, 72)), dtype=dtype, device="cuda")
+    out = torch.empty_like(x)
+    norm(x, out)
+    want = plain.rms_norm(x.double().cpu().numpy(), w.double().numpy(), 2e-4, rnd)
+    np.testing.assert_allclose(out.double().cpu().numpy(), want, atol=tol, rtol=tol)
+    # position
+    rope = build_part("position", q.PartSpec("rope", {"head_dim": 24, "theta": 777.0, "max_positions": 300}))
+    rope.prepare(300, "cuda")
+    cos, sin = plain.rope_table(300, 24, 777.0)
+    np.testing.assert_array_equal(rope.cos.double().cpu().numpy(), cos)
+    np.testing.assert_array_equal(rope.sin.double().cpu().numpy(), sin)
+    qh = torch.tensor(rng.normal(0, 1, (4, 3, 24)), dtype=dtype, device="cuda")
+    kh = torch.tensor(rng.normal(0, 1, (4, 1, 24)), dtype=dtype, device="cuda")
+    pos = torch.tensor([0, 7, 150, 299], dtype=torch.int32, device="cuda")
+    want_q = plain.apply_rope(qh.double().cpu().numpy(), pos.cpu().numpy(), cos, sin, rnd)
+    want_k = plain.apply_rope(kh.double().cpu().numpy(), pos.cpu().numpy(), cos, sin, rnd)
+    rope.apply_(qh, kh, pos)
+    np.testing.assert_allclose(qh.double().cpu().numpy(), want_q, atol=tol, rtol=0)
+    np.testing.assert_allclose(kh.double().cpu().numpy(), want_k, atol=tol, rtol=0)
+    # feed-forward
+    ff = build_part("feed_forward", q.PartSpec("swiglu", {"hidden_size": 48, "intermediate_size": 104, "prefix": "mlp."}))
+    weights = {k: torch.tensor(rng.normal(0, 0.2, s.shape), dtype=dtype, device="cuda")
+               for k, s in ff.weight_specs("L.").items()}
+    as_np = {k: v.double().cpu().numpy() for k, v in weights.items()}
+    ff.bind(dict(weights), "L.", dtype, "cuda")
+    cache = KVCache([], 64, 64, dtype, "cuda")
+    slot = cache.alloc_slot()
+    ctx, _ = context_for(cache, [slot], [9], np.zeros(9), dtype)
+    x = torch.tensor(rng.normal(0, 1, (9, 48)), dtype=dtype, device="cuda")
+    got = ff.forward(x, ctx)
+    want = plain.mlp(x.double().cpu().numpy(), as_np, "L.", rnd)
+    np.testing.assert_allclose(got.double().cpu().numpy(), want, atol=tol * 3, rtol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_mixer_and_block_parts(dtype, tmp_path):
+    """The attention part and the pre-norm block built from a plan's specs, stepped in two
+    pieces over a real cache, against the plain layer."""
+    import qwen3_b200 as q
+    from qwen3_b200.cache.storage import KVCache
+    from qwen3_b200.parts import build_part
+    cfg = tiny("C")
+    _, weights = make_folder(tmp_path, cfg, seed=9)
+    plan = q.config_from_dict(cfg).plan()
+    spec = plan.layers[1]
+    mixer = build_part("mixer", spec.mixer)
+    block = build_part("block", spec.block, mixer, build_part("feed_forward", spec.feed_forward))
+    tensors = {k: torch.tensor(v, dtype=dtype, device="cuda") for k, v in weights.items()}
+    block.bind(dict(tensors), spec.prefix, dtype, "cuda")
+    cache = KVCache([mixer.cache_need()], 192, 192, dtype, "cuda")
+    slot = cache.alloc_slot()
+    rng = np.random.default_rng(1)
+    T, H = 150, cfg["hidden_size"]
+    x = rng.normal(0, 1, (T, H))
+    x = torch.tensor(x, dtype=dtype, device="cuda").double().cpu().numpy()      # what the device holds
+    rnd = plain.identity if dtype == torch.float32 else plain.round_bf16
+    cos, sin = plain.rope_table(T, cfg["head_dim"], cfg["rope_theta"])
+    want = plain.decoder_layer(x, np.arange(T), cfg, weights, 1, cos, sin, rnd)
+    got = np.zeros((T, H))
+    for a, b in ((0, 100), (100, 150)):
+        ctx, step = context_for(cache, [slot], [b - a], np.zeros(b - a), dtype)
+        residual = torch.tensor(x[a:b], dtype=dtype, device="cuda")
+        residual, delta = block.forward(residual, None, ctx, cache.layer(0))
+        got[a:b] = (residual.double() + delta.double()).cpu().numpy()
+        cache.commit(step)
+    tol = 5e-5 if dtype == torch.float32 else 4.0 * np.max(np.abs(want - plain.decoder_layer(
+        x, np.arange(T), cfg, weights, 1, cos, sin, plain.identity))) + 2e-2
+    assert np.max(np.abs(got - want)) <= tol
+
+
+# ----------------------------------------------------------------------------- a toy mixer with state
+class RunningMeanMixer:
+    """out_t = W . mean(x_0 .. x_t): needs no keys, only a fixed-size state per sequence
+    (the running sum and the count).  Written against the documented mixer interface."""
+
+    def __init__(self, hidden_size, prefix="mean."):
+        self.hidden_size, self.prefix, self.weight = hidden_size, prefix, None
+
+    def weight_specs(self, prefix):
+        from qwen3_b200 import WeightSpec
+        return {prefix + self.prefix + "proj.weight": WeightSpec((self.hidden_size, self.hidden_size))}
+
+    def bind(self, weights, prefix, dtype, device):
+        self.weight = weights.pop(prefix + self.prefix + "proj.weight")
+
+    def cache_need(self):
+        from qwen3_b200 import CacheNeed
+        return CacheNeed("none", state_shape=(self.hidden_size + 1,))
+
+    def forward(self, x, ctx, cache):
+        H = self.hidden_size
+        out = ctx.scratch.get("toy.out", (ctx.n_tokens, H), ctx.dtype)
+        if ctx.is_decode:      # device-only arithmetic: safe inside a captured step
+            slots = ctx.seq_slots.long()
+            state = cache.state[slots]
+            state[:, :H] += x.float()
+            state[:, H] += 1.0
+            cache.state[slots] = state
+            mean = state[:, :H] / state[:, H:]
+        else:
+            mean = torch.empty(ctx.n_tokens, H, dtype=torch.float32, device=x.device)
+            start = 0
+            for slot, n in zip(ctx.host_slots, ctx.host_n_new):
+                state = cache.state[slot]
+                sums = state[:H] + torch.cumsum(x[start:start + n].float(), dim=0)
+                counts = state[H] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+                mean[start:start + n] = sums / counts[:, None]
+                state[:H], state[H] = sums[-1], counts[-1]
+                start += n
+        out.copy_(torch.mm(mean.to(self.weight.dtype), self.weight.t()))
+        return out
+
+
+def toy_plain_forward(cfg, w, tokens, toy_layers):
+    x = plain.embedding(tokens, w["model.embed_tokens.weight"])
+    T = len(tokens)
+    cos, sin = plain.rope_table(T, cfg["head_dim"], cfg["rope_theta"])
+    for layer in range(cfg["num_hidden_layers"]):
+        prefix = f"model.layers.{layer}."
+        if layer in toy_layers:
+            a = plain.rms_norm(x, w[prefix + "input_layernorm.weight"], cfg["rms_norm_eps"])
+            mean = np.cumsum(a, axis=0) / np.arange(1, T + 1)[:, None]
+            x = x + mean @ w[prefix + "mean.proj.weight"].T
+            m = plain.rms_norm(x, w[prefix + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+            x = x + plain.mlp(m, w, prefix)
+        else:
+            x = plain.decoder_layer(x, np.arange(T), cfg, w, layer, cos, sin)
+    x = plain.rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+    return plain.linear(x, plain.output_weight(cfg, w))
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    """One model, different mixers in different layers (attention, running mean, attention), in
+    32-bit: whole, token by token and in unequal batches with reused slots agree with the plain
+    restatement."""
+    import qwen3_b200 as q
+    from qwen3_b200.engine.engine import Engine
+    q.register_part("mixer", "running_mean", RunningMeanMixer)
+    cfg = tiny("B")
+    config = q.config_from_dict(cfg)
+    plan = config.plan()
+    toy = dataclasses.replace(plan.layers[1], mixer=q.PartSpec("running_mean", {"hidden_size": cfg["hidden_size"]}))
+    plan = dataclasses.replace(plan, layers=[plan.layers[0], toy, plan.layers[2]])
+    model = q.build_model(plan)
+    specs = model.weight_specs()
+    assert "model.layers.1.mean.proj.weight" in specs and "model.layers.1.self_attn.q_proj.weight" not in specs
+    needs = model.cache_needs()
+    assert needs[1].kind == "none" and needs[1].state_shape == (cfg["hidden_size"] + 1,) and needs[0].kind == "full"
+    tensors = q.random_weights(specs, seed=5, dtype=torch.float32)
+    weights = {k: v.double().numpy() for k, v in tensors.items()}
+    model.bind({k: v for k, v in tensors.items()}, torch.float32, "cuda")
+    rng = np.random.default_rng(2)
+    requests = {f"r{i}": [int(t) for t in rng.integers(0, cfg["vocab_size"], n)] for i, n in enumerate([40, 7, 90, 33, 65])}
+    from test_engine_gpu import run_steps
+    for builder in (schedules.whole, lambda r: schedules.tail_one_by_one(r, 32),
+                    lambda r: schedules.batched(r, {"r0": 8, "r1": 7, "r2": 64, "r3": 1, "r4": 33}, 2)):
+        steps, rows = builder(requests)
+        engine = Engine(model, config, max_tokens=schedules.peak_tokens(steps))
+        got = run_steps(engine, steps, rows)
+        for rid, toks in requests.items():
+            want = toy_plain_forward(cfg, weights, toks, toy_layers={1})
+            for p in range(len(toks)):
+                if (rid, p) in got:
+                    assert np.max(np.abs(got[(rid, p)] - want[p])) <= 1e-4, (rid, p)
+
+
+def test_layer_order_is_data_and_a_layer_can_read_another_layers_cache(tmp_path):
+    """order = [0, 1, 0]: layer 0 runs twice on its one cache... is not a sensible model, so the
+    check here is the cache-sharing one: layer 2 reads layer 0's keys instead of its own."""
+    import qwen3_b200 as q
+    from qwen3_b200.engine.engine import Engine
+    cfg = tiny("B")
+    config = q.config_from_dict(cfg)
+    plan = config.plan()
+    shared = dataclasses.replace(plan, layers=[plan.layers[0], plan.layers[1],
+                                               dataclasses.replace(plan.layers[2], cache_from=0)])
+    model = q.build_model(shared)
+    assert model.cache_needs()[2] is None and model.cache_sources() == {2: 0}
+    tensors = q.random_weights(model.weight_specs(), seed=6, dtype=torch.float32)
+    model.bind(dict(tensors), torch.float32, "cuda")
+    engine = Engine(model, config, max_tokens=128)
+    assert len(engine.cache.groups[0].layers) == 2              # storage for layers 0 and 1 only
+    assert engine.cache.layer(2).keys is engine.cache.layer(0).keys and engine.cache.layer(2).shared
+    s = engine.new_sequence()
+    a = engine.step([q.StepEntry(s, [5, 6, 7, 8], [3])]).cpu().numpy().copy()
+    engine.release(s)
+    s = engine.new_sequence()
+    engine.step([q.StepEntry(s, [5, 6, 7], [])])
+    b = engine.step([q.StepEntry(s, [8], [0])]).cpu().numpy()
+    assert np.all(np.isfinite(a)) and np.max(np.abs(a - b)) <= 2e-5
