@@ -127,9 +127,12 @@ static int rms_norm_launch(T* x, const T* delta, const float* w, T* y, int64_t r
 }
 
 // ---------------------------------------------------------------- SiLU(gate) * up
-// gate_up: [rows, 2*inter] with the gate in the first `inter` columns; out: [rows, inter].
+// gate_up: [rows, 2*inter]; out: [rows, inter].  Two layouts of a row: the gate in the first
+// `inter` columns and the up values in the rest, or (interleaved) blocks of eight gate
+// columns followed by the eight up columns of the same features.
 template <typename T, int VEC>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t rows, int inter) {
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t rows, int inter,
+                                int interleaved) {
     pdl_launch_dependents();
     pdl_wait();
     const int64_t per_row = inter / VEC;
@@ -138,8 +141,10 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
         const int64_t r = i / per_row;
         const int c = (int)(i % per_row) * VEC;
         float g[VEC], u[VEC];
-        load_vec<T, VEC>(gate_up + r * 2 * inter + c, g);
-        load_vec<T, VEC>(gate_up + r * 2 * inter + inter + c, u);
+        const int64_t gate_at = interleaved ? (int64_t)(c >> 3) * 16 + (c & 7) : c;
+        const int64_t up_at = interleaved ? gate_at + 8 : (int64_t)inter + c;
+        load_vec<T, VEC>(gate_up + r * 2 * inter + gate_at, g);
+        load_vec<T, VEC>(gate_up + r * 2 * inter + up_at, u);
 #pragma unroll
         for (int k = 0; k < VEC; ++k) g[k] = round_to<T>(g[k] / (1.0f + expf(-g[k]))) * u[k];
         store_vec<T, VEC>(out + r * inter + c, g);
@@ -147,9 +152,9 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 }
 
 template <typename T>
-static int silu_mul_launch(const T* gate_up, T* out, int64_t rows, int inter, cudaStream_t stream) {
+static int silu_mul_launch(const T* gate_up, T* out, int64_t rows, int inter, int interleaved, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (inter <= 0) return Q3_ERR_BAD_SIZE;
+    if (inter <= 0 || (interleaved && inter % 8 != 0)) return Q3_ERR_BAD_SIZE;
     constexpr int V = Pack<T>::N;
     const bool vec = inter % V == 0 && aligned16(gate_up) && aligned16(out);
     const int threads = 256;
@@ -158,8 +163,9 @@ static int silu_mul_launch(const T* gate_up, T* out, int64_t rows, int inter, cu
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (vec)
         return (int)q3_launch(silu_mul_kernel<T, V>, dim3((unsigned)blocks), dim3(threads), 0, stream, gate_up, out, rows,
-                              inter);
-    return (int)q3_launch(silu_mul_kernel<T, 1>, dim3((unsigned)blocks), dim3(threads), 0, stream, gate_up, out, rows, inter);
+                              inter, interleaved);
+    return (int)q3_launch(silu_mul_kernel<T, 1>, dim3((unsigned)blocks), dim3(threads), 0, stream, gate_up, out, rows, inter,
+                          interleaved);
 }
 
 // ---------------------------------------------------------------- gather rows (+ pending branch)
@@ -197,8 +203,9 @@ static int gather_rows_launch(const T* x, const T* delta, const int* idx, T* out
         return rms_norm_launch<T>((T*)x, (const T*)delta, w, (T*)y, rows, size, eps, x_stride, y_stride,            \
                                   (cudaStream_t)stream);                                                            \
     }                                                                                                               \
-    Q3_EXPORT int q3_silu_mul_##SUFFIX(const void* gate_up, void* out, int64_t rows, int inter, void* stream) {     \
-        return silu_mul_launch<T>((const T*)gate_up, (T*)out, rows, inter, (cudaStream_t)stream);                   \
+    Q3_EXPORT int q3_silu_mul_##SUFFIX(const void* gate_up, void* out, int64_t rows, int inter, int interleaved,    \
+                                       void* stream) {                                                              \
+        return silu_mul_launch<T>((const T*)gate_up, (T*)out, rows, inter, interleaved, (cudaStream_t)stream);      \
     }                                                                                                               \
     Q3_EXPORT int q3_gather_rows_##SUFFIX(const void* x, const void* delta, const int* idx, void* out, int64_t rows, \
                                           int size, void* stream) {                                                 \

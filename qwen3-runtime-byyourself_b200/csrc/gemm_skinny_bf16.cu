@@ -36,9 +36,12 @@ template <> __device__ __forceinline__ float to_out<float>(float v) { return v; 
 template <> __device__ __forceinline__ bf16 to_out<bf16>(float v) { return __float2bfloat16_rn(v); }
 
 // MT: tiles of 8 batch rows (M <= 8*MT).  R: tiles of 16 rows of W per block.  WARPS: K is split
-// over them.  PF: k-blocks (of 32) a warp keeps in flight in registers.
-template <int MT, int R, int WARPS, int PF, typename OutT>
-__global__ void __launch_bounds__(WARPS * 32)
+// over them.  PF: k-blocks (of 32) a warp keeps in flight in registers.  MINB: blocks per SM the
+// register budget is held to, so that the whole grid is resident at once for the layer sizes.
+// GATED: W holds gate and up rows interleaved in blocks of eight (rows 16t..16t+7 gate, 16t+8..
+// 16t+15 up, both for features 8t..8t+7); the kernel then writes round(silu(g)) * u, [M, N/2].
+template <int MT, int R, int WARPS, int PF, int MINB, bool GATED, typename OutT>
+__global__ void __launch_bounds__(WARPS * 32, MINB)
 gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT* __restrict__ Y, int M, int N, int K) {
     extern __shared__ __align__(16) float red[];   // [WARPS][8*MT][16*R + 1]
     constexpr int ROWS = 16 * R, COLS = 8 * MT, LD = ROWS + 1;
@@ -125,63 +128,91 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT*
             mine[(c + 1) * LD + n + 8] = acc[r][m][3];
         }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < ROWS * COLS; idx += WARPS * 32) {
-        const int n = idx % ROWS, m = idx / ROWS;
-        if (m >= M || n0 + n >= N) continue;
-        float sum = 0.0f;
+    if constexpr (!GATED) {
+        for (int idx = threadIdx.x; idx < ROWS * COLS; idx += WARPS * 32) {
+            const int n = idx % ROWS, m = idx / ROWS;
+            if (m >= M || n0 + n >= N) continue;
+            float sum = 0.0f;
 #pragma unroll
-        for (int w2 = 0; w2 < WARPS; ++w2) sum += red[w2 * COLS * LD + m * LD + n];
-        Y[(int64_t)m * N + n0 + n] = to_out<OutT>(sum);
+            for (int w2 = 0; w2 < WARPS; ++w2) sum += red[w2 * COLS * LD + m * LD + n];
+            Y[(int64_t)m * N + n0 + n] = to_out<OutT>(sum);
+        }
+    } else {
+        // feature f = (row tile) * 8 + j has its gate in row 16t + j and its up in row 16t + 8 + j; both
+        // sums are rounded to bfloat16 as the two separate products of the reference would be, then
+        // round(silu(g)) * u as in src/ops/elementwise.cu:47-65
+        constexpr int FEATS = ROWS / 2;
+        const int half_n = N >> 1;
+        for (int idx = threadIdx.x; idx < FEATS * COLS; idx += WARPS * 32) {
+            const int f = idx % FEATS, m = idx / FEATS;
+            const int n = (f >> 3) * 16 + (f & 7);
+            const int feature = (n0 >> 1) + f;
+            if (m >= M || feature >= half_n) continue;
+            float g = 0.0f, u = 0.0f;
+#pragma unroll
+            for (int w2 = 0; w2 < WARPS; ++w2) {
+                g += red[w2 * COLS * LD + m * LD + n];
+                u += red[w2 * COLS * LD + m * LD + n + 8];
+            }
+            g = round_to<bf16>(g);
+            u = round_to<bf16>(u);
+            Y[(int64_t)m * half_n + feature] = to_out<OutT>(round_to<bf16>(g / (1.0f + expf(-g))) * u);
+        }
     }
 }
 
-template <int MT, int R, int WARPS, typename OutT>
+template <int MT, int R, bool GATED, typename OutT>
 int launch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, cudaStream_t stream) {
+    constexpr int WARPS = 8;
+    constexpr int PF = (4 / (R * MT)) < 1 ? 1 : (4 / (R * MT));
+    constexpr int MINB = MT == 1 ? 3 : 2;
     constexpr int SMEM = WARPS * 8 * MT * (16 * R + 1) * 4;
-    constexpr int PF = (8 / (R * MT)) < 2 ? 2 : (8 / (R * MT));
     static bool configured = false;
     if (SMEM > 48 * 1024 && !configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, R, WARPS, PF, OutT>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, R, WARPS, PF, MINB, GATED, OutT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const int blocks = (N + 16 * R - 1) / (16 * R);
-    return (int)q3_launch(gemm_skinny_kernel<MT, R, WARPS, PF, OutT>, dim3(blocks), dim3(WARPS * 32), SMEM, stream, X, W,
-                          Y, M, N, K);
+    return (int)q3_launch(gemm_skinny_kernel<MT, R, WARPS, PF, MINB, GATED, OutT>, dim3(blocks), dim3(WARPS * 32), SMEM,
+                          stream, X, W, Y, M, N, K);
 }
 
-template <typename OutT>
+template <bool GATED, typename OutT>
 int dispatch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 != 0 || M > 64) return Q3_ERR_BAD_SIZE;
+    if (K <= 0 || K % 8 != 0 || M > 64 || (GATED && N % 16 != 0)) return Q3_ERR_BAD_SIZE;
     if (!aligned16(X) || !aligned16(W)) return Q3_ERR_MISALIGNED;
-    // rows of W per block: as many as still leave about two blocks per SM
-    const int r = N >= 16 * 4 * 296 ? 4 : (N >= 16 * 2 * 296 ? 2 : 1);
-    const bool wide = N < 16 * 296 && K >= 2048;   // few blocks: more warps per block share K
+    // rows of W per block: the fewest (16, 32 or 64) with which the grid is resident at once
+    // (three blocks on each of 148 SMs); beyond that the largest
+    const int tiles = (N + 15) / 16;
+    const int r = tiles <= 444 ? 1 : (tiles <= 888 ? 2 : 4);
     if (M <= 8) {
-        if (r == 4) return launch<1, 4, 8, OutT>(X, W, Y, M, N, K, stream);
-        if (r == 2) return launch<1, 2, 8, OutT>(X, W, Y, M, N, K, stream);
-        return wide ? launch<1, 1, 16, OutT>(X, W, Y, M, N, K, stream) : launch<1, 1, 8, OutT>(X, W, Y, M, N, K, stream);
+        if (r == 4) return launch<1, 4, GATED, OutT>(X, W, Y, M, N, K, stream);
+        if (r == 2) return launch<1, 2, GATED, OutT>(X, W, Y, M, N, K, stream);
+        return launch<1, 1, GATED, OutT>(X, W, Y, M, N, K, stream);
     }
     if (M <= 16) {
-        if (r == 4) return launch<2, 4, 8, OutT>(X, W, Y, M, N, K, stream);
-        if (r == 2) return launch<2, 2, 8, OutT>(X, W, Y, M, N, K, stream);
-        return wide ? launch<2, 1, 16, OutT>(X, W, Y, M, N, K, stream) : launch<2, 1, 8, OutT>(X, W, Y, M, N, K, stream);
+        if (r == 4) return launch<2, 4, GATED, OutT>(X, W, Y, M, N, K, stream);
+        if (r == 2) return launch<2, 2, GATED, OutT>(X, W, Y, M, N, K, stream);
+        return launch<2, 1, GATED, OutT>(X, W, Y, M, N, K, stream);
     }
-    if (M <= 32) {
-        if (r >= 2) return launch<4, 2, 8, OutT>(X, W, Y, M, N, K, stream);
-        return wide ? launch<4, 1, 16, OutT>(X, W, Y, M, N, K, stream) : launch<4, 1, 8, OutT>(X, W, Y, M, N, K, stream);
-    }
-    return wide ? launch<8, 1, 16, OutT>(X, W, Y, M, N, K, stream) : launch<8, 1, 8, OutT>(X, W, Y, M, N, K, stream);
+    if (M <= 32) return r >= 2 ? launch<4, 2, GATED, OutT>(X, W, Y, M, N, K, stream) : launch<4, 1, GATED, OutT>(X, W, Y, M, N, K, stream);
+    return launch<8, 1, GATED, OutT>(X, W, Y, M, N, K, stream);
 }
 
 }  // namespace
 
 Q3_EXPORT int q3_gemm_skinny_bf16(const void* X, const void* W, void* Y, int M, int N, int K, void* stream) {
-    return dispatch<bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, (cudaStream_t)stream);
+    return dispatch<false, bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, (cudaStream_t)stream);
 }
 
 Q3_EXPORT int q3_gemm_skinny_bf16_f32out(const void* X, const void* W, void* Y, int M, int N, int K, void* stream) {
-    return dispatch<float>((const bf16*)X, (const bf16*)W, (float*)Y, M, N, K, (cudaStream_t)stream);
+    return dispatch<false, float>((const bf16*)X, (const bf16*)W, (float*)Y, M, N, K, (cudaStream_t)stream);
+}
+
+// W [N, K] holds gate and up rows interleaved in blocks of eight; Y [M, N/2] = round(silu(g)) * u.
+Q3_EXPORT int q3_gemm_skinny_gated_bf16(const void* X, const void* W, void* Y, int M, int N, int K, void* stream) {
+    return dispatch<true, bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, (cudaStream_t)stream);
 }

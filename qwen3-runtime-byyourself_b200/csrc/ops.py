@@ -140,14 +140,17 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[r, c] = silu(gate_up[r, c]) * gate_up[r, inter + c]."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
+    """out[r, c] = silu(gate[r, c]) * up[r, c]; a row of `gate_up` holds the gate in its first half
+    and the up values in its second, or (`interleaved`) blocks of eight gate columns each followed
+    by the eight up columns of the same features."""
     s = _suffix(gate_up)
     rows, two_i = gate_up.shape
     if two_i % 2 or out.shape != (rows, two_i // 2) or out.dtype != gate_up.dtype:
         raise KernelError("silu_mul: output does not fit")
-    fn = _fn("elementwise.cu", f"q3_silu_mul_{s}", [c_void_p, c_void_p, c_int64, c_int, c_void_p])
-    _check(fn(_dev(gate_up, "gate_up"), _dev(out, "out"), rows, two_i // 2, _stream()), "silu_mul")
+    fn = _fn("elementwise.cu", f"q3_silu_mul_{s}", [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p])
+    _check(fn(_dev(gate_up, "gate_up"), _dev(out, "out"), rows, two_i // 2, int(bool(interleaved)), _stream()),
+           "silu_mul")
     return out
 
 
@@ -370,3 +373,24 @@ def gemm_tcgen05_splitk(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scr
            "gemm_tcgen05_splitk")
     _count_extra(1)
     return out
+
+
+def gemm_skinny_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N/2] = round(silu(g)) * u where g and u are the products of x with the gate and up rows of
+    w [N, K], which holds them interleaved in blocks of eight rows (see `interleave_gate_up`)."""
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N // 2) or N % 16 != 0 or not gemm_skinny_fits(M, K):
+        raise KernelError(f"gemm_skinny_gated: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    fn = _fn("gemm_skinny_bf16.cu", "q3_gemm_skinny_gated_bf16", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out", torch.bfloat16), M, N, K,
+              _stream()), "gemm_skinny_gated")
+    return out
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[2I, K]: rows 16t..16t+7 are gate rows 8t..8t+7, rows 16t+8..16t+15 the up rows of the same features."""
+    I, K = gate.shape
+    if I % 8 != 0 or up.shape != gate.shape:
+        raise KernelError("interleave_gate_up: the intermediate size must be a multiple of 8")
+    return torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()

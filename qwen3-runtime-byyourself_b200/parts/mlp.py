@@ -1,8 +1,9 @@
 """SwiGLU feed-forward as a part: down( silu(gate(x)) * up(x) ).
 
 Reference: src/model/mlp.cpp:101-115 (three products and one elementwise kernel) and
-src/ops/elementwise.cu:47-65.  Here gate and up run as one product over the row-wise
-concatenation [Wg; Wu] made at bind time.
+src/ops/elementwise.cu:47-65.  Here gate and up run as one product over one matrix made
+at bind time, their rows interleaved in blocks of eight; for the few rows of a decode
+step the product's kernel applies SiLU and the gating itself.
 """
 from __future__ import annotations
 
@@ -11,6 +12,7 @@ import torch
 from ..csrc import ops
 from ..weights.loader import WeightSpec
 from .base import Part, register_part
+from . import linear as linear_module
 from .linear import linear
 
 
@@ -26,16 +28,23 @@ class SwiGLU(Part):
 
     def bind(self, weights: dict, prefix: str, dtype, device) -> None:
         p = prefix + self.prefix
-        self.w_gate_up = torch.cat([weights.pop(p + "gate_proj.weight"), weights.pop(p + "up_proj.weight")],
-                                   dim=0).contiguous()
+        gate, up = weights.pop(p + "gate_proj.weight"), weights.pop(p + "up_proj.weight")
+        # gate and up rows interleaved in blocks of eight: one product gives both, and a kernel that owns
+        # 16 consecutive output rows can finish silu(g) * u itself
+        self.interleaved = self.intermediate_size % 8 == 0
+        self.w_gate_up = ops.interleave_gate_up(gate, up) if self.interleaved else torch.cat([gate, up], dim=0).contiguous()
         self.w_down = weights.pop(p + "down_proj.weight").contiguous()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         N, I = ctx.n_tokens, self.intermediate_size
-        gate_up = ctx.scratch.get("ff.gate_up", (N, 2 * I), ctx.dtype)
-        linear(x, self.w_gate_up, gate_up)
         act = ctx.scratch.get("ff.act", (N, I), ctx.dtype)
-        ops.silu_mul(gate_up, act)
+        if (self.interleaved and ctx.dtype == torch.bfloat16 and N <= linear_module.skinny_rows
+                and ops.gemm_skinny_fits(N, self.hidden_size)):
+            ops.gemm_skinny_gated(x, self.w_gate_up, act)          # product, SiLU and gating in one kernel
+        else:
+            gate_up = ctx.scratch.get("ff.gate_up", (N, 2 * I), ctx.dtype)
+            linear(x, self.w_gate_up, gate_up)
+            ops.silu_mul(gate_up, act, self.interleaved)
         out = ctx.scratch.get("ff.out", (N, self.hidden_size), ctx.dtype)
         return linear(act, self.w_down, out)
 

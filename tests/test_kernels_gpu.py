@@ -445,3 +445,34 @@ def test_tcgen05_split_k_product(M, N, K, splits):
         err = (out.double() - want).abs().max().item()
         bound = 4e-5 * math.sqrt(K) * 4 if out_dtype == "float32" else 0.02 * math.sqrt(K)
         assert err <= bound, f"max abs err {err:.3e} > {bound:.3e}"
+
+
+@pytest.mark.parametrize("M,inter,K", [(1, 64, 64), (8, 12288, 4096), (3, 160, 96), (16, 1000, 256), (9, 112, 80)])
+def test_gated_skinny_product_and_interleaved_silu(M, inter, K):
+    """gate/up rows interleaved in blocks of eight: the fused kernel (product + SiLU + gating) and the
+    two-kernel path (product, then silu_mul on the interleaved layout) agree with the plain formula."""
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(M + inter + K)
+    xd = dev(rng.normal(0, 1, (M, K)), "bfloat16")
+    gate, up = dev(rng.normal(0, 0.2, (inter, K)), "bfloat16"), dev(rng.normal(0, 0.2, (inter, K)), "bfloat16")
+    w = ops.interleave_gate_up(gate, up)
+    g = plain.round_bf16(back(xd) @ back(gate).T)
+    u = plain.round_bf16(back(xd) @ back(up).T)
+    want = plain.silu_multiply(g, u, plain.round_bf16)
+    fused = torch.empty(M, inter, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_skinny_gated(xd, w, fused)
+    gate_up = torch.empty(M, 2 * inter, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_skinny(xd, w, gate_up)
+    two = torch.empty_like(fused)
+    ops.silu_mul(gate_up, two, interleaved=True)
+    scale = max(1.0, float(np.abs(want).max()))
+    assert np.max(np.abs(back(fused) - want)) <= 2e-2 * scale
+    assert np.max(np.abs(back(two) - want)) <= 2e-2 * scale
+    assert torch.equal(fused, two)                      # same sums, same rounding points
+    # and the 32-bit elementwise kernel on the interleaved layout
+    gu32 = torch.tensor(rng.normal(0, 2, (M, 2 * inter)), dtype=torch.float32, device="cuda")
+    out32 = torch.empty(M, inter, dtype=torch.float32, device="cuda")
+    ops.silu_mul(gu32, out32, interleaved=True)
+    blocks = back(gu32).reshape(M, inter // 8, 2, 8)
+    np.testing.assert_allclose(back(out32), plain.silu_multiply(blocks[:, :, 0, :].reshape(M, inter),
+                                                                blocks[:, :, 1, :].reshape(M, inter)), atol=1e-5, rtol=1e-5)
