@@ -209,6 +209,195 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The prompt form: persistent, tokens first.  D[128 tokens, BN rows of W] per tile, so a thread of
+// the epilogue owns one token and writes a contiguous run of outputs.  Each block walks tiles
+// (tile = blockIdx.x, += gridDim.x; the token tile varies fastest so that blocks running at the
+// same time share W tiles in the L2); the accumulator is double-buffered in tensor memory
+// (2 x BN columns), so the epilogue of one tile runs under the products of the next.
+constexpr uint32_t make_idesc_mn(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+        "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+
+template <typename OutT> __device__ __forceinline__ void store_run8(OutT* p, const uint32_t* r);
+template <> __device__ __forceinline__ void store_run8<float>(float* p, const uint32_t* r) {
+    reinterpret_cast<uint4*>(p)[0] = make_uint4(r[0], r[1], r[2], r[3]);
+    reinterpret_cast<uint4*>(p)[1] = make_uint4(r[4], r[5], r[6], r[7]);
+}
+template <> __device__ __forceinline__ void store_run8<bf16>(bf16* p, const uint32_t* r) {
+    uint4 v;
+    __nv_bfloat162 t;
+    t = __floats2bfloat162_rn(__uint_as_float(r[0]), __uint_as_float(r[1])); v.x = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(__uint_as_float(r[2]), __uint_as_float(r[3])); v.y = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(__uint_as_float(r[4]), __uint_as_float(r[5])); v.z = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(__uint_as_float(r[6]), __uint_as_float(r[7])); v.w = *reinterpret_cast<uint32_t*>(&t);
+    *reinterpret_cast<uint4*>(p) = v;
+}
+
+// GATED: W holds gate and up rows interleaved in blocks of eight (as the decode kernel's gated form);
+// the epilogue then writes round(silu(g)) * u, [M, N/2], instead of the raw product.
+template <int BN, int STAGES, bool GATED, typename OutT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                           OutT* __restrict__ Y, int M, int N, int K, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN;      // two accumulators
+    static_assert(2 * BN <= 512, "two accumulators have to fit the 512 columns of tensor memory");
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = base + STAGES * STAGE_BYTES;       // full[S], empty[S], acc_full[2], acc_empty[2], slot
+    const uint32_t bar_acc_full = bars + 2 * STAGES * 8, bar_acc_empty = bar_acc_full + 16, tmem_slot = bar_acc_empty + 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN, tiles = m_tiles * n_tiles;
+    const int nkb = (K + BK - 1) / BK;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bars + s * 8, 1);
+            mbar_init(bars + (STAGES + s) * 8, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_acc_full + b * 8, 1);
+            mbar_init(bar_acc_empty + b * 8, 4);             // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_wait();                                       // X is the output of the kernel before
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(bars + (STAGES + s) * 8, ((it / STAGES) & 1u) ^ 1u);
+                    if (!ok) { atomicExch(status, 1); break; }
+                    const uint32_t a = base + s * STAGE_BYTES, b = a + A_BYTES;
+                    mbar_expect_tx(bars + s * 8, STAGE_BYTES);
+                    tma_load_2d(a, &map_x, bars + s * 8, kb * BK, m0);
+                    tma_load_2d(b, &map_w, bars + s * 8, kb * BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_mn(BM, BN);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+                const uint32_t buf = local & 1u;
+                ok = mbar_wait(bar_acc_empty + buf * 8, ((local >> 1) & 1u) ^ 1u);      // the epilogue has drained it
+                if (!ok) { atomicExch(status, 4); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(bars + s * 8, (it / STAGES) & 1u);
+                    if (!ok) { atomicExch(status, 2); break; }
+                    tc_fence_after();
+                    const uint32_t a = base + s * STAGE_BYTES, b = a + A_BYTES;
+                    const uint64_t da = make_desc(a), db = make_desc(b);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc_mma(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(bars + (STAGES + s) * 8);
+                }
+                tc_commit(bar_acc_full + buf * 8);
+            }
+        }
+    } else {
+        pdl_wait();
+        const int lane_base = (warp & 3) * 32;
+        const bool vec_ok = ((GATED ? (N >> 1) : N) % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15u) == 0);
+        uint32_t local = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+            const uint32_t buf = local & 1u;
+            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+            if (!mbar_wait(bar_acc_full + buf * 8, (local >> 1) & 1u)) {
+                if (lane == 0) atomicExch(status, 3);
+                break;
+            }
+            tc_fence_after();
+            const int m = m0 + lane_base + lane;
+            OutT* row = Y + (int64_t)m * (GATED ? (N >> 1) : N) + (GATED ? (n0 >> 1) : n0);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tc_ld32(tmem_base + ((uint32_t)lane_base << 16) + buf * BN + (uint32_t)c, r);
+                tc_wait_ld();
+                if constexpr (GATED) {
+                    // columns c..c+31 = gate[8] up[8] gate[8] up[8] of 16 features (src/ops/elementwise.cu:47-65)
+                    if (m < M) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int n = n0 + c + h * 16;           // first gate column of this block
+                            uint32_t packed[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const float g = round_to<bf16>(__uint_as_float(r[h * 16 + e]));
+                                const float u = round_to<bf16>(__uint_as_float(r[h * 16 + 8 + e]));
+                                packed[e] = __float_as_uint(round_to<bf16>(g / (1.0f + expf(-g))) * u);
+                            }
+                            OutT* dst = row + ((c + h * 16) >> 1);
+                            if (n + 16 <= N && vec_ok) {
+                                store_run8<OutT>(dst, packed);
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e)
+                                    if (n + 8 + e < N) dst[e] = to_out<OutT>(__uint_as_float(packed[e]));
+                            }
+                        }
+                    }
+                } else if (m < M) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        const int n = n0 + c + j;
+                        if (vec_ok && n + 8 <= N) {
+                            store_run8<OutT>(row + c + j, r + j);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                if (n + e < N) row[c + j + e] = to_out<OutT>(__uint_as_float(r[j + e]));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty + buf * 8);          // this warp's quarter is drained
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // out[m, n] = sum over splits of part[s, m, n], in split order.
 template <typename OutT>
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, OutT* __restrict__ out, int64_t count, int splits) {
@@ -267,7 +456,56 @@ int launch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int split
                           Y, M, N, K, status);
 }
 
+template <int BN, int STAGES, bool GATED, typename OutT>
+int launch_prompt(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int* status, cudaStream_t stream) {
+    constexpr int SMEM = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+    static bool configured = false;
+    static int sm_count = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_prompt_kernel<BN, STAGES, GATED, OutT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+        configured = true;
+    }
+    CUtensorMap map_x, map_w;
+    if (!make_map(&map_x, X, M, K, BM) || !make_map(&map_w, W, N, K, BN)) return Q3_ERR_BAD_SIZE;
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int blocks = tiles < sm_count ? tiles : sm_count;
+    return (int)q3_launch(gemm_tcgen05_prompt_kernel<BN, STAGES, GATED, OutT>, dim3(blocks), dim3(THREADS), (size_t)SMEM, stream,
+                          map_x, map_w, Y, M, N, K, status);
+}
+
 }  // namespace
+
+// The prompt form: persistent blocks, 128 tokens x `tile_n` (128 or 256) rows of W per tile.
+Q3_EXPORT int q3_gemm_tcgen05_prompt_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32,
+                                          int tile_n, int* status, void* stream_) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0) return Q3_ERR_BAD_SIZE;
+    if (!aligned16(X) || !aligned16(W)) return Q3_ERR_MISALIGNED;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const bf16* x = (const bf16*)X;
+    const bf16* w = (const bf16*)W;
+    if (tile_n == 256)
+        return out_is_f32 ? launch_prompt<256, 4, false, float>(x, w, (float*)Y, M, N, K, status, stream)
+                          : launch_prompt<256, 4, false, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
+    if (tile_n == 128)
+        return out_is_f32 ? launch_prompt<128, 6, false, float>(x, w, (float*)Y, M, N, K, status, stream)
+                          : launch_prompt<128, 6, false, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
+    return Q3_ERR_BAD_SIZE;
+}
+
+// W [N, K] holds gate and up rows interleaved in blocks of eight; Y [M, N/2] = round(silu(g)) * u, bfloat16.
+Q3_EXPORT int q3_gemm_tcgen05_prompt_gated_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int* status,
+                                                void* stream_) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || N % 16 != 0) return Q3_ERR_BAD_SIZE;
+    if (!aligned16(X) || !aligned16(W)) return Q3_ERR_MISALIGNED;
+    return launch_prompt<256, 4, true, bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, status, (cudaStream_t)stream_);
+}
 
 // Direct product (one K range per tile).  `tile_n` picks the token tile: 16, 32, 64, 128 or 256.
 // `status` is a device int that a kernel sets to 1/2/3 if a bounded wait ran out (0 otherwise).

@@ -394,3 +394,34 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     if I % 8 != 0 or up.shape != gate.shape:
         raise KernelError("interleave_gate_up: the intermediate size must be a multiple of 8")
     return torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
+
+
+def gemm_tcgen05_prompt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_n: int = 256) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T for many rows: persistent blocks, tiles of 128 tokens by `tile_n`
+    (128 or 256) rows of w, accumulators double-buffered in tensor memory."""
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N) or K % 8 != 0:
+        raise KernelError(f"gemm_tcgen05_prompt: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_tcgen05_prompt: output must be bfloat16 or float32")
+    fn = _fn("gemm_tcgen05.cu", "q3_gemm_tcgen05_prompt_bf16",
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), M, N, K,
+              int(out.dtype == torch.float32), int(tile_n), _status_word(x.device).data_ptr(), _stream()),
+           "gemm_tcgen05_prompt")
+    return out
+
+
+def gemm_tcgen05_prompt_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N/2] = round(silu(g)) * u for many rows; `w` [N, K] holds the gate and up rows interleaved in
+    blocks of eight (`interleave_gate_up`); the gating runs in the product's epilogue."""
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N // 2) or K % 8 != 0 or N % 16 != 0 or out.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_tcgen05_prompt_gated: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    fn = _fn("gemm_tcgen05.cu", "q3_gemm_tcgen05_prompt_gated_bf16",
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), M, N, K,
+              _status_word(x.device).data_ptr(), _stream()), "gemm_tcgen05_prompt_gated")
+    return out

@@ -288,6 +288,15 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def check_kernels(self) -> None:
+        """Raise if a bounded wait inside a kernel gave up since the last check.  Reads one word
+        from the device: call it where the host waits for the device anyway."""
+        from ..csrc import ops
+        where = ops.tcgen05_status(self.device)
+        if where:
+            raise ops.KernelError(f"a wait inside the tcgen05 product ran out (stage {where}: 1 producer, 2 MMA, "
+                                  f"3 epilogue, 4 accumulator); its results are not valid")
+
     # -- the step
     def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run the given tokens of every entry as one batch, append them to the cache and return

@@ -90,6 +90,8 @@ def generate(engine, prompts: Sequence[Sequence[int]], chooser, max_new_tokens: 
                 entries = [StepEntry(slot, feed[i], [len(feed[i]) - 1]) for i, slot in live]
                 logits = engine.step(entries)
                 chosen = chooser.choose(logits, [i for i, _ in live], [step_index] * len(live))
+                if step_index % 32 == 0 and hasattr(engine, "check_kernels"):
+                    engine.check_kernels()            # now and then: a kernel whose bounded wait ran out is reported
                 still = []
                 for (i, slot), token in zip(live, chosen):
                     token = int(token)
@@ -107,6 +109,8 @@ def generate(engine, prompts: Sequence[Sequence[int]], chooser, max_new_tokens: 
                     engine.release(slot)
                 live = still
                 step_index += 1
+            if hasattr(engine, "check_kernels"):
+                engine.check_kernels()
         except BaseException:
             for _, slot in live:
                 try:

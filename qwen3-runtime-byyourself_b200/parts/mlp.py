@@ -41,6 +41,9 @@ class SwiGLU(Part):
         if (self.interleaved and ctx.dtype == torch.bfloat16 and N <= linear_module.skinny_rows
                 and ops.gemm_skinny_fits(N, self.hidden_size)):
             ops.gemm_skinny_gated(x, self.w_gate_up, act)          # product, SiLU and gating in one kernel
+        elif (self.interleaved and ctx.dtype == torch.bfloat16 and N >= linear_module.prompt_rows
+                and self.hidden_size % 8 == 0):
+            ops.gemm_tcgen05_prompt_gated(x, self.w_gate_up, act)  # the gating runs in the product's epilogue
         else:
             gate_up = ctx.scratch.get("ff.gate_up", (N, 2 * I), ctx.dtype)
             linear(x, self.w_gate_up, gate_up)
