@@ -1,0 +1,401 @@
+// Causal grouped-query attention for prompts on the 5th-generation tensor cores (bfloat16):
+// S = Q.K^T and O += P.V are tcgen05.mma with the accumulators in tensor memory; Q, K and V
+// tiles arrive by TMA straight from the packed query buffer and from the cache pages.
+//
+// Same math as the reference's kernel (src/ops/gqa_attention.cu:84-153: causal by bound, scale
+// after the dot, online softmax and weighted sum in 32-bit), arranged for Blackwell:
+//   grid (tile of 128 new tokens, query head, sequence); three roles per block
+//   warp 0     TMA: the Q tile once, then one cache page (64 keys: K and V panels of the head's
+//              kv group, two 64-column halves each at head size 128) per stage of a ring
+//   warp 1     one thread issues the products: S(j) = Q.K_j^T into TMEM columns [0,64), then
+//              O += P_j.V_j with P read from TMEM and V as an MN-major shared-memory operand;
+//              S(j+1) is issued as soon as the softmax warps have read S(j)
+//   warps 2-5  softmax: thread r owns query row r (TMEM lane r): loads its 64 scores, masks the
+//              diagonal page, keeps a running maximum that is only raised when the new maximum
+//              exceeds it by more than 2^8 (the accumulator is then rescaled in TMEM), writes
+//              P as packed bfloat16 into TMEM columns [64,96), and at the end normalises O
+// Every mbarrier wait is bounded and reports into `status`.  Head sizes 64 and 128, no window;
+// other shapes use the mma.sync kernel of attention_prefill.cu.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#ifndef Q3_HEAD_DIM
+#error "compile with -DQ3_HEAD_DIM=<64 or 128>"
+#endif
+
+namespace {
+
+constexpr int D = Q3_HEAD_DIM;
+static_assert(D == 64 || D == 128, "the tcgen05 attention takes head sizes 64 and 128");
+constexpr int PAGE = 64, BM = 128, HALVES = D / 64;
+constexpr int THREADS = 192;
+constexpr int STAGES = 2;
+constexpr int Q_BYTES = HALVES * BM * 128;               // 128 rows x 128 bytes per half
+constexpr int PANEL_BYTES = HALVES * PAGE * 128;         // one page of K (or V): 64 keys x 128 bytes per half
+constexpr int STAGE_BYTES = 2 * PANEL_BYTES;
+constexpr int SMEM_BYTES = Q_BYTES + STAGES * STAGE_BYTES + 1024 + 256;
+constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t COL_S = 0, COL_P = 64, COL_O = 128;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+constexpr float RESCALE_THRESHOLD = 8.0f;                // in log2 units: probabilities stay below 2^8
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] . B[smem]
+__device__ __forceinline__ void tc_mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+// D[tmem] (+)= A[tmem] . B[smem]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+        "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+        "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// K-major operand (rows of 128 bytes, 128-byte swizzle, eight-row groups 1024 bytes apart).
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// MN-major operand: 64 contiguous elements of the N dimension per 128-byte row, one row per k;
+// eight-k groups 1024 bytes apart (stride offset), the next 64 elements of N `chunk_bytes` further
+// (leading offset).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t chunk_bytes) {
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((chunk_bytes >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::f16 instruction descriptor: float32 accumulator, bfloat16 operands; bit 16 = B is MN-major.
+constexpr uint32_t idesc(int m, int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(THREADS)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ seq_start,
+                  const int* __restrict__ seq_pos0, const int* __restrict__ page_table, int pages_per_seq, int nq, int nkv,
+                  float scale_log2, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    pdl_launch_dependents();
+    pdl_wait();
+    // the last tiles of a sequence see the most keys: they are scheduled first
+    const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
+    const int t0 = seq_start[seq], n_new = seq_start[seq + 1] - t0;
+    if (tile * BM >= n_new) return;
+    const int kvh = head / (nq / nkv);
+    const int pos0 = seq_pos0[seq];
+    const int* pages = page_table + (int64_t)seq * pages_per_seq;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rows = min(BM, n_new - tile * BM);
+    const int n_pages = (pos0 + tile * BM + rows - 1) / PAGE + 1;        // pages 0 .. the one of the last row
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_smem = base, kv_smem = base + Q_BYTES;
+    const uint32_t bars = kv_smem + STAGES * STAGE_BYTES;
+    const uint32_t bar_q = bars, bar_kv_full = bars + 8, bar_kv_empty = bar_kv_full + 8 * STAGES;
+    const uint32_t bar_s_full = bar_kv_empty + 8 * STAGES, bar_s_read = bar_s_full + 8, bar_p_full = bar_s_read + 8;
+    const uint32_t bar_pv_done = bar_p_full + 8, tmem_slot = bar_pv_done + 8;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_q, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_kv_full + 8 * s, 1);
+            mbar_init(bar_kv_empty + 8 * s, 1);
+        }
+        mbar_init(bar_s_full, 1);
+        mbar_init(bar_s_read, 4);
+        mbar_init(bar_p_full, 4);
+        mbar_init(bar_pv_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem) : "r"(tmem_slot) : "memory");
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_expect_tx(bar_q, Q_BYTES);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) tma_load_2d(q_smem + h * BM * 128, &map_q, bar_q, head * D + h * 64, t0 + tile * BM);
+            for (int j = 0; j < n_pages; ++j) {
+                const int s = j % STAGES;
+                if (!mbar_wait(bar_kv_empty + 8 * s, ((uint32_t)(j / STAGES) & 1u) ^ 1u)) { atomicExch(status, 11); break; }
+                const uint32_t k_dst = kv_smem + s * STAGE_BYTES, v_dst = k_dst + PANEL_BYTES;
+                const int row = (pages[j] * nkv + kvh) * PAGE;
+                mbar_expect_tx(bar_kv_full + 8 * s, STAGE_BYTES);
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) {
+                    tma_load_2d(k_dst + h * PAGE * 128, &map_k, bar_kv_full + 8 * s, h * 64, row);
+                    tma_load_2d(v_dst + h * PAGE * 128, &map_v, bar_kv_full + 8 * s, h * 64, row);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = idesc(BM, PAGE, false), idesc_pv = idesc(BM, D, true);
+            auto issue_s = [&](int j) {
+                const uint32_t k_src = kv_smem + (j % STAGES) * STAGE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * (BM * 128) + (kk & 3) * 32, koff = (kk >> 2) * (PAGE * 128) + (kk & 3) * 32;
+                    tc_mma_ss(tmem + COL_S, desc_k_major(q_smem + off), desc_k_major(k_src + koff), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                tc_commit(bar_s_full);
+            };
+            bool ok = mbar_wait(bar_q, 0) && mbar_wait(bar_kv_full, 0);
+            if (!ok) atomicExch(status, 12);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0);
+            }
+            for (int j = 0; j < n_pages && ok; ++j) {
+                // S(j+1) may overwrite the score columns once the softmax warps hold S(j) in registers
+                if (j + 1 < n_pages) {
+                    ok = mbar_wait(bar_s_read, (uint32_t)j & 1u) &&
+                         mbar_wait(bar_kv_full + 8 * ((j + 1) % STAGES), (uint32_t)((j + 1) / STAGES) & 1u);
+                    if (!ok) { atomicExch(status, 13); break; }
+                    tc_fence_after();
+                    issue_s(j + 1);
+                }
+                ok = mbar_wait(bar_p_full, (uint32_t)j & 1u);                 // P(j) is in TMEM, O is rescaled
+                if (!ok) { atomicExch(status, 14); break; }
+                tc_fence_after();
+                const uint32_t v_src = kv_smem + (j % STAGES) * STAGE_BYTES + PANEL_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < PAGE / 16; ++kk)
+                    tc_mma_ts(tmem + COL_O, tmem + COL_P + kk * 8, desc_mn_major(v_src + kk * 16 * 128, PAGE * 128), idesc_pv,
+                              (j > 0 || kk > 0) ? 1u : 0u);
+                tc_commit(bar_kv_empty + 8 * (j % STAGES));                   // the page's K and V are consumed
+                tc_commit(bar_pv_done);
+            }
+        }
+    } else {
+        // ------------------------------------------------ softmax and epilogue: thread = query row
+        const int lane_base = (warp & 3) * 32;
+        const int r = lane_base + lane;                                     // row of the tile
+        const int p_row = pos0 + tile * BM + r;                             // its absolute position
+        const uint32_t t_row = tmem + ((uint32_t)lane_base << 16);
+        float m_run = -INFINITY, l_run = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_pages && ok; ++j) {
+            ok = mbar_wait(bar_s_full, (uint32_t)j & 1u);
+            if (!ok) { if (lane == 0) atomicExch(status, 15); break; }
+            tc_fence_after();
+            uint32_t s[64];
+            tc_ld32(t_row + COL_S, s);
+            tc_ld32(t_row + COL_S + 32, s + 32);
+            tc_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_s_read);
+            const int key0 = j * PAGE;
+            const bool edge = key0 + PAGE - 1 > pos0 + tile * BM;           // some key of the page lies after some row
+            float m_page = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+                float v = __uint_as_float(s[c]) * scale_log2;
+                if (edge && key0 + c > p_row) v = -INFINITY;
+                s[c] = __float_as_uint(v);
+                m_page = fmaxf(m_page, v);
+            }
+            float alpha = 1.0f;
+            bool raise = false;
+            if (j == 0) {
+                m_run = m_page == -INFINITY ? 0.0f : m_page;                 // the first page overwrites O: nothing to rescale
+            } else if (m_page > m_run + RESCALE_THRESHOLD) {
+                alpha = exp2f(m_run - m_page);
+                m_run = m_page;
+                raise = true;
+            }
+            float sum = 0.0f;
+            uint32_t p[32];
+#pragma unroll
+            for (int c = 0; c < 64; c += 2) {
+                const float a = exp2f(__uint_as_float(s[c]) - m_run), b = exp2f(__uint_as_float(s[c + 1]) - m_run);
+                sum += a + b;
+                p[c >> 1] = pack_bf16(a, b);
+            }
+            l_run = l_run * alpha + sum;
+            if (j > 0) {
+                ok = mbar_wait(bar_pv_done, (uint32_t)(j - 1) & 1u);         // O and the P columns are free again
+                if (!ok) { if (lane == 0) atomicExch(status, 16); break; }
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, raise)) {                        // the loads and stores are warp-wide
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 32) {
+                        uint32_t o[32];
+                        tc_ld32(t_row + COL_O + c, o);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                        tc_st32(t_row + COL_O + c, o);
+                    }
+                }
+            }
+            tc_st32(t_row + COL_P, p);
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_p_full);
+        }
+        if (ok) {
+            ok = mbar_wait(bar_pv_done, (uint32_t)(n_pages - 1) & 1u);
+            if (!ok && lane == 0) atomicExch(status, 17);
+        }
+        if (ok) {
+            tc_fence_after();
+            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            bf16* dst = out + ((int64_t)(t0 + tile * BM + r) * nq + head) * D;
+#pragma unroll 1
+            for (int c = 0; c < D; c += 32) {
+                uint32_t o[32];
+                tc_ld32(t_row + COL_O + c, o);
+                tc_wait_ld();
+                if (r < rows) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        uint4 v;
+                        v.x = pack_bf16(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+                        v.y = pack_bf16(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
+                        v.z = pack_bf16(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
+                        v.w = pack_bf16(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c + e) = v;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// [rows, cols] bfloat16 row-major, fetched in boxes of [box_rows, 64 columns] with 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int box_rows) {
+    EncodeTiled fn = encode_fn();
+    if (fn == nullptr) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+Q3_EXPORT int q3_attention_prefill_tc_head_dim() { return D; }
+
+// q: [n_tokens, nq * D]; k_pages, v_pages: [n_cache_pages, nkv, 64, D]; out: [n_tokens, nq * D].
+Q3_EXPORT int q3_attention_prefill_tc_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                           const int* seq_start, const int* seq_pos0, const int* page_table,
+                                           int pages_per_seq, int n_seqs, int max_new, int64_t n_tokens,
+                                           int64_t n_cache_pages, int nq, int nkv, float scale, int* status, void* stream) {
+    if (n_seqs <= 0 || max_new <= 0) return 0;
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0) return Q3_ERR_BAD_SIZE;
+    if (n_seqs > 65535 || nq > 65535) return Q3_ERR_TOO_LARGE;
+    if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(out)) return Q3_ERR_MISALIGNED;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    CUtensorMap map_q, map_k, map_v;
+    if (!make_map(&map_q, q, n_tokens, (int64_t)nq * D, BM) || !make_map(&map_k, k_pages, n_cache_pages * nkv * PAGE, D, PAGE) ||
+        !make_map(&map_v, v_pages, n_cache_pages * nkv * PAGE, D, PAGE))
+        return Q3_ERR_BAD_SIZE;
+    const dim3 grid((max_new + BM - 1) / BM, nq, n_seqs);
+    return (int)q3_launch(prefill_tc_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)stream, map_q, map_k, map_v,
+                          (bf16*)out, seq_start, seq_pos0, page_table, pages_per_seq, nq, nkv, scale * 1.4426950408889634f,
+                          status);
+}

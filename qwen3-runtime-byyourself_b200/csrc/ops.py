@@ -425,3 +425,25 @@ def gemm_tcgen05_prompt_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tenso
     _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), M, N, K,
               _status_word(x.device).data_ptr(), _stream()), "gemm_tcgen05_prompt_gated")
     return out
+
+
+# ------------------------------------------------------------------ bfloat16 prompt attention on tcgen05
+def attention_prefill_tc_fits(d: int, window: Optional[int]) -> bool:
+    return d in (64, 128) and not window
+
+
+def attention_prefill_tc(q, k_pages, v_pages, out, seq_start, seq_pos0, page_table, n_seqs: int, max_new: int,
+                         n_tokens: int, nq: int, nkv: int, d: int, scale: float):
+    """Causal attention of every new token over its pages with both products on tcgen05 (TMA-fed,
+    scores and output accumulated in tensor memory).  Head sizes 64 and 128."""
+    if q.dtype != torch.bfloat16 or not attention_prefill_tc_fits(d, None):
+        raise KernelError("attention_prefill_tc: bfloat16, head size 64 or 128")
+    fn = _fn("attention_prefill_tc.cu", "q3_attention_prefill_tc_bf16",
+             [c_void_p] * 7 + [c_int, c_int, c_int, c_int64, c_int64, c_int, c_int, c_float, c_void_p, c_void_p],
+             defines=(f"Q3_HEAD_DIM={d}",))
+    _check(fn(_dev(q, "q"), _dev(k_pages, "k_pages", torch.bfloat16), _dev(v_pages, "v_pages", torch.bfloat16),
+              _dev(out, "out", torch.bfloat16), _dev(seq_start, "seq_start", torch.int32),
+              _dev(seq_pos0, "seq_pos0", torch.int32), _dev(page_table, "page_table", torch.int32),
+              page_table.shape[-1], n_seqs, max_new, n_tokens, k_pages.shape[0], nq, nkv, float(scale),
+              _status_word(q.device).data_ptr(), _stream()), "attention_prefill_tc")
+    return out

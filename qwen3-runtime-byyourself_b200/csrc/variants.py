@@ -13,4 +13,5 @@ def all_variants():
         ("attention_prefill.cu", ("Q3_HEAD_DIM=128",)),
         ("attention_decode_static.cu", ("Q3_HEAD_DIM=128",)),
         ("gemm_tcgen05.cu", ()),
+        ("attention_prefill_tc.cu", ("Q3_HEAD_DIM=128",)),
     ]

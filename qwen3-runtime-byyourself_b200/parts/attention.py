@@ -133,7 +133,21 @@ def _prefill_flash_kernel(part, q, cache, out, ctx, table) -> bool:
     return True
 
 
+def _prefill_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
+    """Both products of the attention on tcgen05 with TMA-fed tiles: head sizes 64 and 128, no window,
+    and enough new tokens for 128-row tiles to be worth it."""
+    if not ops.attention_prefill_tc_fits(part.head_dim, part.window) or ctx.max_new < tc_prefill_rows:
+        return False
+    ops.attention_prefill_tc(q[:ctx.n_tokens], cache.keys, cache.values, out, ctx.seq_start, ctx.seq_pos0, table,
+                             ctx.n_seqs, ctx.max_new, ctx.n_tokens, part.num_heads, part.num_kv_heads, part.head_dim,
+                             part.scale)
+    return True
+
+
+tc_prefill_rows = 128     # from this many new tokens of the longest sequence on, the tcgen05 kernel runs
+
 DECODE_KERNELS.append(_decode_split_kernel)
+PREFILL_KERNELS.append(_prefill_tcgen05_kernel)
 PREFILL_KERNELS.append(_prefill_flash_kernel)
 
 register_part("mixer", "gqa_attention", GQAAttention)

@@ -519,3 +519,47 @@ def test_tcgen05_prompt_gated_epilogue(M, inter, K):
     ud = plain.round_bf16(back(x) @ back(up).T)
     want = plain.silu_multiply(gd, ud, plain.round_bf16)
     assert np.max(np.abs(back(fused) - want)) <= 2e-2 * max(1.0, float(np.abs(want).max()))
+
+
+@pytest.mark.parametrize("nq,nkv,d", [(8, 2, 128), (4, 4, 64), (6, 1, 128)])
+def test_prefill_attention_tcgen05_kernel(nq, nkv, d):
+    """The TMA + tcgen05 attention: prompts of unequal length in one launch, then a second launch
+    that continues them from the cache, over shuffled pages, against float64 causal attention.
+    One sequence carries a score pattern that forces the running maximum to be raised late."""
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(nq * 17 + d)
+    lengths, first = [700, 5, 129, 64, 333, 1000], [256, 1, 100, 63, 130, 999]
+    table, kp, vp = paged_case(rng, lengths, nkv, d, "bfloat16")
+    table_d = torch.as_tensor(table).cuda()
+    full = [rng.normal(0, 1, (n, (nq + 2 * nkv) * d)) for n in lengths]
+    # late keys with much larger scores than early ones: the accumulator has to be rescaled in TMEM
+    full[0][600:, nq * d:(nq + nkv) * d] *= 6.0
+    got = [np.zeros((n, nq * d)) for n in lengths]
+    for part in range(2):
+        spans = [(0, f) if part == 0 else (f, n) for f, n in zip(first, lengths)]
+        rows = np.concatenate([full[s][a:b] for s, (a, b) in enumerate(spans)])
+        seq = np.concatenate([np.full(b - a, s) for s, (a, b) in enumerate(spans)]).astype(np.int32)
+        pos = np.concatenate([np.arange(a, b) for a, b in spans]).astype(np.int32)
+        starts = np.cumsum([0] + [b - a for a, b in spans]).astype(np.int32)
+        N = rows.shape[0]
+        q = torch.empty(N, nq * d, dtype=torch.bfloat16, device="cuda")
+        out = torch.zeros_like(q)
+        seq_d, pos_d = torch.as_tensor(seq).cuda(), torch.as_tensor(pos).cuda()
+        ops.qkv_prepare(dev(rows, "bfloat16"), q, kp, vp, None, None, None, None, seq_d, pos_d, table_d, N, nq, nkv, d, 0.0)
+        ops.attention_prefill_tc(q, kp, vp, out, torch.as_tensor(starts).cuda(),
+                                 torch.as_tensor([a for a, _ in spans], dtype=torch.int32).cuda(), table_d, len(lengths),
+                                 max(b - a for a, b in spans), N, nq, nkv, d, d ** -0.5)
+        assert ops.tcgen05_status("cuda") == 0, "a wait inside the kernel gave up"
+        o = back(out)
+        k = 0
+        for s, (a, b) in enumerate(spans):
+            got[s][a:b] = o[k:k + b - a]
+            k += b - a
+    for s, n in enumerate(lengths):
+        x = stored(full[s], "bfloat16")
+        qs = x[:, :nq * d].reshape(n, nq, d)
+        ks = x[:, nq * d:(nq + nkv) * d].reshape(n, nkv, d)
+        vs = x[:, (nq + nkv) * d:].reshape(n, nkv, d)
+        want = plain.gqa_attention(qs, ks, vs).reshape(n, nq * d)
+        err = np.abs(got[s] - want).max(axis=1)
+        assert err.max() <= 2e-2, f"sequence {s}: row {int(err.argmax())} of {n}: max abs err {err.max():.3e}"
