@@ -3,7 +3,7 @@
 //
 // In the reference every projection is one cublasGemmEx call whatever M is
 // (src/ops/linear.cpp:165-193).  With M <= 64 the product is bound by reading W once, so
-// this kernel is built around that stream: a block owns 16*R rows of W and splits K over
+// this kernel is built around that stream: a block owns 16 rows of W and splits K over
 // its warps; every lane reads 16 contiguous bytes of a W row per step and feeds them
 // straight to the tensor cores as the 16-row operand of mma.m16n8k16, with the batch rows
 // as the 8-column operand.  Since a sum over k does not care about the order of k, the
@@ -161,11 +161,8 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT*
     }
 }
 
-template <int MT, int R, bool GATED, typename OutT>
+template <int MT, int R, int WARPS, int PF, int MINB, bool GATED, typename OutT>
 int launch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, cudaStream_t stream) {
-    constexpr int WARPS = 8;
-    constexpr int PF = (4 / (R * MT)) < 1 ? 1 : (4 / (R * MT));
-    constexpr int MINB = MT == 1 ? 3 : 2;
     constexpr int SMEM = WARPS * 8 * MT * (16 * R + 1) * 4;
     static bool configured = false;
     if (SMEM > 48 * 1024 && !configured) {
@@ -179,27 +176,27 @@ int launch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, cudaStrea
                           stream, X, W, Y, M, N, K);
 }
 
+// The shapes below come from a sweep over (rows per block, k-blocks in flight, blocks per SM, warps)
+// on the projections of an 8B-sized layer at batch 8: 16 rows of W per block always won; matrices of
+// few rows (one block per SM or less) want 16 warps sharing K, the others 8 warps and three blocks per SM.
 template <bool GATED, typename OutT>
 int dispatch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || M > 64 || (GATED && N % 16 != 0)) return Q3_ERR_BAD_SIZE;
     if (!aligned16(X) || !aligned16(W)) return Q3_ERR_MISALIGNED;
-    // rows of W per block: the fewest (16, 32 or 64) with which the grid is resident at once
-    // (three blocks on each of 148 SMs); beyond that the largest
-    const int tiles = (N + 15) / 16;
-    const int r = tiles <= 444 ? 1 : (tiles <= 888 ? 2 : 4);
-    if (M <= 8) {
-        if (r == 4) return launch<1, 4, GATED, OutT>(X, W, Y, M, N, K, stream);
-        if (r == 2) return launch<1, 2, GATED, OutT>(X, W, Y, M, N, K, stream);
-        return launch<1, 1, GATED, OutT>(X, W, Y, M, N, K, stream);
-    }
-    if (M <= 16) {
-        if (r == 4) return launch<2, 4, GATED, OutT>(X, W, Y, M, N, K, stream);
-        if (r == 2) return launch<2, 2, GATED, OutT>(X, W, Y, M, N, K, stream);
-        return launch<2, 1, GATED, OutT>(X, W, Y, M, N, K, stream);
-    }
-    if (M <= 32) return r >= 2 ? launch<4, 2, GATED, OutT>(X, W, Y, M, N, K, stream) : launch<4, 1, GATED, OutT>(X, W, Y, M, N, K, stream);
-    return launch<8, 1, GATED, OutT>(X, W, Y, M, N, K, stream);
+    const bool few_rows = (N + 15) / 16 <= 296;
+    if (M <= 8)
+        return few_rows ? launch<1, 1, 16, 2, 2, GATED, OutT>(X, W, Y, M, N, K, stream)
+                        : launch<1, 1, 8, 4, 3, GATED, OutT>(X, W, Y, M, N, K, stream);
+    if (M <= 16)
+        return few_rows ? launch<2, 1, 16, 2, 1, GATED, OutT>(X, W, Y, M, N, K, stream)
+                        : launch<2, 1, 8, 2, 3, GATED, OutT>(X, W, Y, M, N, K, stream);
+    // the split of K over warps depends on N alone, so a row's sum has the same order for every M
+    if (M <= 32)
+        return few_rows ? launch<4, 1, 16, 1, 1, GATED, OutT>(X, W, Y, M, N, K, stream)
+                        : launch<4, 1, 8, 2, 2, GATED, OutT>(X, W, Y, M, N, K, stream);
+    return few_rows ? launch<8, 1, 16, 1, 1, GATED, OutT>(X, W, Y, M, N, K, stream)
+                    : launch<8, 1, 8, 1, 2, GATED, OutT>(X, W, Y, M, N, K, stream);
 }
 
 }  // namespace

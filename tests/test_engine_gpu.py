@@ -180,3 +180,32 @@ def test_step_errors_leave_the_cache_unchanged(folders):
     assert engine.step([StepEntry(s, [1, 2, 3], [])]) is None
     assert engine.length(s) == 3
     engine.release(s)
+
+
+def test_8b_layer_shapes_in_32_bit_match_the_plain_model():
+    """One layer of the Qwen3-8B shape (hidden 4096, 32/8 heads of 128, intermediate 12288, vocabulary
+    151936) in true 32-bit: whole, cut in two, and token by token agree with the float64 plain model to
+    1e-4.  TF32 or bfloat16 anywhere on the path would miss this bound by orders of magnitude."""
+    import torch
+    import qwen3_b200 as q
+    cfg = dict(tiny("B"), num_hidden_layers=1, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+               head_dim=128, intermediate_size=12288, vocab_size=151936, max_position_embeddings=4096,
+               bos_token_id=151643, eos_token_id=151645, torch_dtype="bfloat16")
+    config = q.config_from_dict(cfg)
+    model = q.build_model(config.plan())
+    tensors = q.random_weights(model.weight_specs(), seed=8, dtype=torch.bfloat16, device="cuda")
+    weights = {k: v.double().cpu().numpy() for k, v in tensors.items()}
+    model.bind(tensors, torch.float32, "cuda")
+    from qwen3_b200.engine.engine import Engine
+    engine = Engine(model, config, max_tokens=128, max_seq_len=128)
+    rng = np.random.default_rng(3)
+    toks = random_tokens(rng, 9, cfg["vocab_size"])
+    exact = plain_logits(cfg, weights, toks)
+    requests = {"r": toks}
+    whole = run_steps(engine, *schedules.whole(requests))
+    one = run_steps(engine, *schedules.tail_one_by_one(requests, 4))
+    for p in range(len(toks)):
+        assert np.max(np.abs(whole[("r", p)] - exact[p])) <= FP32_TOL, p
+        if ("r", p) in one:
+            assert np.max(np.abs(one[("r", p)] - exact[p])) <= FP32_TOL, p
+    assert float(np.abs(exact).max()) > 0.5      # the bound is meaningful: logits are of order one
