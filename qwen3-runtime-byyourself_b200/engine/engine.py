@@ -251,6 +251,7 @@ class Engine:
         # a mixer whose step depends on host values (not only on the context's device fields) opts out
         self.use_graphs = use_graphs and all(getattr(b.mixer, "graph_safe", True) for b in model.blocks)
         self._graphs = {}
+        self.device_tokens = True  # `step` can read a decode step's token ids on the device
         self.launches = 0          # kernels of this library launched by steps (replayed graph nodes included)
         self.last_upload_bytes = 0
 

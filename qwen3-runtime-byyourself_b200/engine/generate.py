@@ -80,6 +80,11 @@ def generate(engine, prompts: Sequence[Sequence[int]], chooser, max_new_tokens: 
     if max_new_tokens == 0 or not prompts:
         return results
     cache = engine.cache
+    if hasattr(chooser, "choose_async") and getattr(engine, "device_tokens", False):
+        for batch in plan_batches([len(p) for p in prompts], max_new_tokens, cache.n_pages, cache.n_slots,
+                                  cache.page_tokens, batch_size):
+            _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_tokens, stops, on_token)
+        return results
     for batch in plan_batches([len(p) for p in prompts], max_new_tokens, cache.n_pages, cache.n_slots,
                               cache.page_tokens, batch_size):
         live = [(i, engine.new_sequence()) for i in batch]
@@ -119,3 +124,74 @@ def generate(engine, prompts: Sequence[Sequence[int]], chooser, max_new_tokens: 
                     pass
             raise
     return results
+
+
+def _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_tokens, stops, on_token) -> None:
+    """One batch with the host one step behind the device.
+
+    The next step is launched before the ids of the current one have reached the host: it reads
+    them on the device, where the sampler wrote them, for every sequence that still has budget.  A
+    sequence whose pending token turns out to be a stop token has then run one step too many; that
+    row is dropped, and its slot goes back like any other.  So the device never waits for the host
+    to look at a token, and the decisions are those of the plain loop."""
+    from ..cache.book import CacheFull
+    live = [(i, engine.new_sequence()) for i in batch]
+    ended = set()
+    try:
+        logits = engine.step([StepEntry(slot, prompts[i], [len(prompts[i]) - 1]) for i, slot in live])
+        pending = chooser.choose_async(logits, [i for i, _ in live], [0] * len(live))
+        step_index = 0
+        while live:
+            onward = [(i, slot) for i, slot in live if i not in ended and len(results[i].token_ids) + 1 < max_new_tokens]
+            upcoming = None
+            if onward:
+                rows = [k for k, (i, _) in enumerate(live) if (i, _) in onward]
+                tokens_on_device = pending.device_ids
+                if rows != list(range(len(live))):
+                    tokens_on_device = tokens_on_device[_index(rows, tokens_on_device.device)]
+                try:
+                    logits = engine.step([StepEntry(slot, [0], [0]) for _, slot in onward],
+                                         device_tokens=tokens_on_device)
+                    upcoming = chooser.choose_async(logits, [i for i, _ in onward], [step_index + 1] * len(onward))
+                except CacheFull:
+                    upcoming = None            # no room to run ahead: fall back to waiting for the ids first
+            chosen = pending.result()
+            if step_index % 32 == 0 and hasattr(engine, "check_kernels"):
+                engine.check_kernels()
+            for (i, slot), token in zip(live, chosen):
+                if i in ended:
+                    continue
+                token = int(token)
+                results[i].token_ids.append(token)
+                if on_token is not None:
+                    on_token(i, token)
+                if token in stops:
+                    results[i].stop_reason = STOP_TOKEN
+                elif len(results[i].token_ids) >= max_new_tokens:
+                    results[i].stop_reason = MAX_NEW_TOKENS
+                else:
+                    continue
+                ended.add(i)
+                engine.release(slot)
+            step_index += 1
+            if onward and upcoming is None:
+                onward = [(i, slot) for i, slot in onward if i not in ended]
+                if onward:
+                    logits = engine.step([StepEntry(slot, [results[i].token_ids[-1]], [0]) for i, slot in onward])
+                    upcoming = chooser.choose_async(logits, [i for i, _ in onward], [step_index] * len(onward))
+            live, pending = (onward, upcoming) if upcoming is not None else ([], None)
+        if hasattr(engine, "check_kernels"):
+            engine.check_kernels()
+    except BaseException:
+        for i, slot in live:
+            if i not in ended:
+                try:
+                    engine.release(slot)
+                except Exception:
+                    pass
+        raise
+
+
+def _index(rows, device):
+    import torch
+    return torch.as_tensor(rows, dtype=torch.long, device=device)

@@ -19,6 +19,20 @@ class NonFiniteLogits(RuntimeError):
     """A row of logits held NaN or Inf (the reference refuses such rows too)."""
 
 
+class PendingChoice:
+    """Ids that are being chosen on the device and copied to the host; `result()` waits for them."""
+
+    def __init__(self, device_ids: torch.Tensor, host_ids: torch.Tensor, event: torch.cuda.Event):
+        self.device_ids, self._host, self._event = device_ids, host_ids, event
+
+    def result(self) -> List[int]:
+        self._event.synchronize()
+        ids = self._host.tolist()
+        if any(i < 0 for i in ids):
+            raise NonFiniteLogits("sampling met a non-finite logit")
+        return ids
+
+
 class Sampler:
     def __init__(self, params: SamplingParams, vocab_size: int, device):
         if params.valid_vocab_size > vocab_size:
@@ -33,11 +47,15 @@ class Sampler:
         if rows <= self._cap:
             return
         self._cap = max(rows, 2 * self._cap)
-        self._out = torch.empty(self._cap, dtype=torch.int32, device=self.device)
-        self._ids_dev = torch.empty(self._cap, dtype=torch.int64, device=self.device)
-        self._steps_dev = torch.empty(self._cap, dtype=torch.int32, device=self.device)
-        self._ids_host = torch.empty(self._cap, dtype=torch.int64).pin_memory()
-        self._steps_host = torch.empty(self._cap, dtype=torch.int32).pin_memory()
+        self._turn = 0
+        self._outs = [torch.empty(self._cap, dtype=torch.int32, device=self.device) for _ in range(2)]
+        self._out_hosts = [torch.empty(self._cap, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._out = self._outs[0]
+        # stream keys go through pinned staging; one set per turn, since two choices can be in flight
+        self._ids_devs = [torch.empty(self._cap, dtype=torch.int64, device=self.device) for _ in range(2)]
+        self._steps_devs = [torch.empty(self._cap, dtype=torch.int32, device=self.device) for _ in range(2)]
+        self._ids_hosts = [torch.empty(self._cap, dtype=torch.int64).pin_memory() for _ in range(2)]
+        self._steps_hosts = [torch.empty(self._cap, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._out_host = torch.empty(self._cap, dtype=torch.int32).pin_memory()
 
     def choose_device(self, logits: torch.Tensor, sequence_ids: Sequence[int], steps: Sequence[int]) -> torch.Tensor:
@@ -48,13 +66,28 @@ class Sampler:
         out = self._out[:rows]
         if self.params.mode == "greedy":
             return ops.argmax(logits, out, valid)
-        self._ids_host[:rows] = torch.as_tensor(list(sequence_ids), dtype=torch.int64)
-        self._steps_host[:rows] = torch.as_tensor(list(steps), dtype=torch.int32)
-        self._ids_dev[:rows].copy_(self._ids_host[:rows], non_blocking=True)
-        self._steps_dev[:rows].copy_(self._steps_host[:rows], non_blocking=True)
+        t = self._turn
+        self._ids_hosts[t][:rows] = torch.as_tensor(list(sequence_ids), dtype=torch.int64)
+        self._steps_hosts[t][:rows] = torch.as_tensor(list(steps), dtype=torch.int32)
+        self._ids_devs[t][:rows].copy_(self._ids_hosts[t][:rows], non_blocking=True)
+        self._steps_devs[t][:rows].copy_(self._steps_hosts[t][:rows], non_blocking=True)
         p = self.params
-        return ops.sample(logits, out, p.temperature, p.top_k, p.top_p, p.seed, self._ids_dev[:rows],
-                          self._steps_dev[:rows], valid)
+        return ops.sample(logits, out, p.temperature, p.top_k, p.top_p, p.seed, self._ids_devs[t][:rows],
+                          self._steps_devs[t][:rows], valid)
+
+    def choose_async(self, logits: torch.Tensor, sequence_ids: Sequence[int], steps: Sequence[int]) -> PendingChoice:
+        """Start the choice and its copy to the host without waiting.  Two results can be in flight: the
+        device ids of one call stay valid until the call after the next."""
+        rows = logits.shape[0]
+        self._grow(rows)
+        self._turn ^= 1
+        self._out = self._outs[self._turn]
+        ids = self.choose_device(logits, sequence_ids, steps)
+        host = self._out_hosts[self._turn][:rows]
+        host.copy_(ids, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return PendingChoice(ids, host, event)
 
     def choose(self, logits: torch.Tensor, sequence_ids: Sequence[int], steps: Sequence[int]) -> List[int]:
         """The chosen ids as Python ints (one device-to-host copy of 4 bytes per row)."""
