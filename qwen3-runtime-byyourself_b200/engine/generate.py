@@ -148,7 +148,7 @@ def _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_token
                 rows = [k for k, (i, _) in enumerate(live) if (i, _) in onward]
                 tokens_on_device = pending.device_ids
                 if rows != list(range(len(live))):
-                    tokens_on_device = tokens_on_device[_index(rows, tokens_on_device.device)]
+                    tokens_on_device = _take(tokens_on_device, rows)
                 try:
                     logits = engine.step([StepEntry(slot, [0], [0]) for _, slot in onward],
                                          device_tokens=tokens_on_device)
@@ -192,6 +192,9 @@ def _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_token
         raise
 
 
-def _index(rows, device):
-    import torch
-    return torch.as_tensor(rows, dtype=torch.long, device=device)
+def _take(ids, rows):
+    """ids[rows] for a device tensor (or, for the stand-ins of the tests, an array)."""
+    if hasattr(ids, "device") and hasattr(ids, "index_select"):
+        import torch
+        return ids.index_select(0, torch.as_tensor(rows, dtype=torch.long, device=ids.device))
+    return ids[rows]

@@ -153,3 +153,52 @@ def test_sampling_params_follow_the_reference_checks():
     us = [q.uniform_for(42, s, t) for s in range(4) for t in range(4)]
     assert all(0.0 <= u < 1.0 for u in us) and len(set(us)) == 16
     assert q.uniform_for(42, 3, 5) == q.uniform_for(42, 3, 5) != q.uniform_for(43, 3, 5)
+
+
+class AheadEngine(ScriptedEngine):
+    """The scripted engine with the device-token path: a decode step may take its token ids from the
+    array the chooser wrote ("on the device") instead of from the entries."""
+    device_tokens = True
+
+    def __init__(self, *a, **k):
+        super().__init__(*a, **k)
+        self.wasted = 0
+
+    def step(self, entries, device_tokens=None):
+        if device_tokens is not None:
+            assert len(device_tokens) == len(entries) and all(list(e.tokens) == [0] for e in entries)
+            entries = [q.StepEntry(e.slot, [int(t)], e.want) for e, t in zip(entries, device_tokens)]
+        return super().step(entries)
+
+
+class AheadArgmax(Argmax):
+    class Pending:
+        def __init__(self, ids):
+            self.device_ids = np.asarray(ids)
+
+        def result(self):
+            return [int(t) for t in self.device_ids]
+
+    def choose_async(self, logits, sequence_ids, steps):
+        return self.Pending(self.choose(logits, sequence_ids, steps))
+
+
+def test_running_ahead_gives_the_same_tokens_and_frees_everything():
+    prompts = [[1, 2, 3], [7], [4, 4, 4, 4, 4, 4, 4], [9, 9], [5]]
+    stops = [28, 22, 5]
+    plain_engine, ahead_engine = ScriptedEngine(), AheadEngine()
+    want = q.generate(plain_engine, prompts, Argmax(), max_new_tokens=9, stop_token_ids=stops)
+    chooser = AheadArgmax()
+    got = q.generate(ahead_engine, prompts, chooser, max_new_tokens=9, stop_token_ids=stops)
+    assert [(r.token_ids, r.stop_reason) for r in got] == [(r.token_ids, r.stop_reason) for r in want]
+    assert ahead_engine.cache.slots.n_free == ahead_engine.cache.n_slots and ahead_engine.cache.pages_held() == 0
+    # a sequence that drew a stop token ran at most one step too many, never more
+    assert len(plain_engine.steps) <= len(ahead_engine.steps) <= len(plain_engine.steps) + 1
+    rows_plain = sum(len(s) for s in plain_engine.steps)
+    rows_ahead = sum(len(s) for s in ahead_engine.steps)
+    n_stopped = sum(r.stop_reason == q.STOP_TOKEN for r in want)
+    assert rows_plain <= rows_ahead <= rows_plain + n_stopped
+    # sequences that reach their budget run no extra step; the random streams are numbered as in the plain loop
+    assert chooser.calls[0] == ([0, 1, 2, 3, 4], [0] * 5) and chooser.calls[1][1][0] == 1
+    again = q.generate(AheadEngine(max_tokens=64 * 2), prompts, AheadArgmax(), max_new_tokens=9, stop_token_ids=stops)
+    assert [r.token_ids for r in again] == [r.token_ids for r in want]       # several batches, slots reused
