@@ -23,6 +23,18 @@ namespace {
 constexpr int PAGE = 64;
 constexpr int MAX_HEAD_DIM = 256;
 
+template <typename T> __device__ __forceinline__ void load_pack_f32(const T* p, float (&v)[Pack<T>::N]) {
+    const Pack<T> k = load_pack<T>(p);
+#pragma unroll
+    for (int i = 0; i < Pack<T>::N; ++i) v[i] = k.get(i);
+}
+template <typename T> __device__ __forceinline__ void store_pack_f32(T* p, const float (&v)[Pack<T>::N]) {
+    Pack<T> k;
+#pragma unroll
+    for (int i = 0; i < Pack<T>::N; ++i) k.set(i, v[i]);
+    store_pack<T>(p, k);
+}
+
 template <typename T>
 __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pages,
                                    T* __restrict__ v_pages, const float* __restrict__ q_norm_w,
@@ -94,6 +106,79 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_
     }
 }
 
+// The same with 16-byte accesses: a head is shared by half/VEC lanes, each of which owns VEC
+// consecutive elements of the first half and the matching VEC of the second half (the two members
+// of every rotation pair), so a warp works on several heads at once.  One warp per group of
+// consecutive (token, head) pairs.
+template <typename T>
+__global__ void qkv_prepare_vec_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pages,
+                                       T* __restrict__ v_pages, const float* __restrict__ q_norm_w,
+                                       const float* __restrict__ k_norm_w, const float* __restrict__ cos_tab,
+                                       const float* __restrict__ sin_tab, const int* __restrict__ token_seq,
+                                       const int* __restrict__ token_pos, const int* __restrict__ page_table,
+                                       int pages_per_seq, int nq, int nkv, int d, float eps, int write_kv,
+                                       int64_t n_tokens) {
+    constexpr int VEC = Pack<T>::N;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int half = d >> 1, lph = half / VEC, hpw = 32 / lph;       // lanes per head, heads per warp
+    const int lane = threadIdx.x & 31, sub = lane % lph, grp = lane / lph;
+    const int heads = nq + 2 * nkv;
+    const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t pair = warp * hpw + grp;                             // flat (token, head) index
+    const bool active = grp < hpw && pair < n_tokens * heads;
+    const int64_t t = active ? pair / heads : 0;
+    const int head = active ? (int)(pair % heads) : 0;
+    const bool is_q = head < nq, is_v = head >= nq + nkv;
+    const bool live = active && (is_q || write_kv);
+    const int pos = token_pos[t];
+    const T* src = qkv + (t * heads + head) * (int64_t)d + sub * VEC;
+    float a[VEC], b[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) a[i] = b[i] = 0.0f;
+    if (live) {
+        load_pack_f32<T>(src, a);
+        load_pack_f32<T>(src + half, b);
+    }
+    const float* norm_w = is_q ? q_norm_w : (is_v ? nullptr : k_norm_w);
+    // the sum over the lanes of a head: every lane of the warp takes part in every shuffle
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) sq += a[i] * a[i] + b[i] * b[i];
+    float total = 0.0f;
+    const int first = grp * lph;
+    for (int j = 0; j < lph; ++j) total += __shfl_sync(0xffffffffu, sq, (first + j) & 31);
+    if (norm_w != nullptr) {
+        const float inv = rsqrtf(total / (float)d + eps);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            a[i] = round_to<T>(round_to<T>(a[i] * inv) * norm_w[sub * VEC + i]);
+            b[i] = round_to<T>(round_to<T>(b[i] * inv) * norm_w[half + sub * VEC + i]);
+        }
+    }
+    if (!live) return;
+    if (cos_tab != nullptr && !is_v) {
+        const float* c = cos_tab + (int64_t)pos * half + sub * VEC;
+        const float* sn = sin_tab + (int64_t)pos * half + sub * VEC;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            const float x = a[i] * c[i] - b[i] * sn[i], y = b[i] * c[i] + a[i] * sn[i];
+            a[i] = x;
+            b[i] = y;
+        }
+    }
+    T* dst;
+    if (is_q) {
+        dst = q_out + (t * nq + head) * (int64_t)d;
+    } else {
+        const int kvh = (head - nq) % nkv;
+        const int page = page_table[(int64_t)token_seq[t] * pages_per_seq + pos / PAGE];
+        dst = (is_v ? v_pages : k_pages) + (((int64_t)page * nkv + kvh) * PAGE + pos % PAGE) * d;
+    }
+    store_pack_f32<T>(dst + sub * VEC, a);
+    store_pack_f32<T>(dst + half + sub * VEC, b);
+}
+
 // One block per (query head, token).  128 threads: the four warps share the keys of a
 // page for the scores; thread t owns output dims t and t + 128.
 template <typename T>
@@ -162,6 +247,17 @@ int qkv_prepare_launch(const T* qkv, T* q_out, T* k_pages, T* v_pages, const flo
                        int write_kv, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (d <= 0 || d % 2 != 0 || d > MAX_HEAD_DIM || nq <= 0 || nkv <= 0) return Q3_ERR_BAD_SIZE;
+    constexpr int VEC = Pack<T>::N;
+    if (n_tokens >= 64 && (d / 2) % VEC == 0 && (d / 2) / VEC <= 32 && aligned16(qkv) && aligned16(q_out) &&
+        aligned16(k_pages) && aligned16(v_pages)) {
+        const int hpw = 32 / ((d / 2) / VEC);
+        const int64_t n_warps = (n_tokens * (nq + 2 * nkv) + hpw - 1) / hpw;
+        const int64_t blocks = (n_warps + 7) / 8;
+        if (blocks > 0x7fffffffLL) return Q3_ERR_TOO_LARGE;
+        return (int)q3_launch(qkv_prepare_vec_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, qkv, q_out, k_pages,
+                              v_pages, q_norm_w, k_norm_w, cos_tab, sin_tab, token_seq, token_pos, page_table, pages_per_seq,
+                              nq, nkv, d, eps, write_kv, n_tokens);
+    }
     if (n_tokens > 65535) return Q3_ERR_TOO_LARGE;
     const int warps = 4;
     const dim3 grid((nq + 2 * nkv + warps - 1) / warps, (unsigned)n_tokens);

@@ -108,6 +108,50 @@ __global__ void rms_norm_kernel(T* __restrict__ x, const T* __restrict__ delta, 
     }
 }
 
+// The same for rows that fit the registers of a block: every thread keeps PER packets of its row, so
+// the row is read once (twice with `delta`) and written once (twice); used for prompts, where the norms
+// are bound by memory traffic.
+template <typename T, int PER>
+__global__ void rms_norm_reg_kernel(T* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ w,
+                                    T* __restrict__ y, int size, float eps, int64_t x_stride, int64_t y_stride) {
+    constexpr int VEC = Pack<T>::N;
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t row = blockIdx.x;
+    T* xr = x + row * x_stride;
+    const T* dr = delta ? delta + row * x_stride : nullptr;
+    T* yr = y + row * y_stride;
+    float v[PER][VEC];
+    float sq = 0.0f;
+#pragma unroll
+    for (int p = 0; p < PER; ++p) {
+        const int c = (p * blockDim.x + threadIdx.x) * VEC;
+        if (c < size) {
+            load_vec<T, VEC>(xr + c, v[p]);
+            if (dr) {
+                float d[VEC];
+                load_vec<T, VEC>(dr + c, d);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) v[p][i] = round_to<T>(v[p][i] + d[i]);
+                store_vec<T, VEC>(xr + c, v[p]);
+            }
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) sq += v[p][i] * v[p][i];
+        }
+    }
+    const float inv = rsqrtf(block_sum(sq, scratch) / (float)size + eps);
+#pragma unroll
+    for (int p = 0; p < PER; ++p) {
+        const int c = (p * blockDim.x + threadIdx.x) * VEC;
+        if (c < size) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) v[p][i] = round_to<T>(v[p][i] * inv) * w[c + i];
+            store_vec<T, VEC>(yr + c, v[p]);
+        }
+    }
+}
+
 template <typename T>
 static int rms_norm_launch(T* x, const T* delta, const float* w, T* y, int64_t rows, int size, float eps,
                            int64_t x_stride, int64_t y_stride, cudaStream_t stream) {
@@ -116,6 +160,20 @@ static int rms_norm_launch(T* x, const T* delta, const float* w, T* y, int64_t r
     constexpr int V = Pack<T>::N;
     const bool vec = size % V == 0 && x_stride % V == 0 && y_stride % V == 0 && aligned16(x) && aligned16(y) &&
                      (delta == nullptr || aligned16(delta));
+    if (vec && rows >= 64) {
+        const int packs = size / V;
+        const int per = (packs + 255) / 256;                       // packets a thread keeps
+        const int threads = ((packs + per - 1) / per + 31) / 32 * 32;
+        if (per == 1)
+            return (int)q3_launch(rms_norm_reg_kernel<T, 1>, dim3((unsigned)rows), dim3(threads), 0, stream, x, delta, w, y,
+                                  size, eps, x_stride, y_stride);
+        if (per == 2)
+            return (int)q3_launch(rms_norm_reg_kernel<T, 2>, dim3((unsigned)rows), dim3(threads), 0, stream, x, delta, w, y,
+                                  size, eps, x_stride, y_stride);
+        if (per <= 4)
+            return (int)q3_launch(rms_norm_reg_kernel<T, 4>, dim3((unsigned)rows), dim3(threads), 0, stream, x, delta, w, y,
+                                  size, eps, x_stride, y_stride);
+    }
     const int per = vec ? V : 1;
     int threads = (size / per + 31) / 32 * 32;
     threads = threads < 32 ? 32 : (threads > 512 ? 512 : threads);
