@@ -11,6 +11,14 @@ Parity with the reference (RicardoMin/Qwen3-Runtime-ByYourself):
 Beyond the reference: torch_dtype may be "float32" as well as "bfloat16" (a
 folder of 32-bit weights for the 32-bit path), and `plan()` states the model as
 data for the parts, the cache and the step function.
+
+`from_dict(root, strict=True)` is the reference's parser key for key.  The default
+(`strict=False`, what `load_config` uses) additionally reads config.json files as
+newer exporters write them: `dtype` for `torch_dtype`, `rope_parameters.rope_theta`
+for `rope_theta`, and it lets the switches that have one possible value here be absent
+(`attention_bias`, `use_sliding_window`, `hidden_act`, `tie_word_embeddings` = false,
+`bos_token_id`, `head_dim` = hidden_size / num_attention_heads).  Every model size and
+`rms_norm_eps` stay required in both modes.
 """
 from __future__ import annotations
 
@@ -68,6 +76,41 @@ def _reject_non_null(root, key):
         raise ConfigError(f"config field '{key}' is not supported and must be null or absent")
 
 
+def _with_defaults(root: dict) -> dict:
+    """The same keys as the strict parser reads, filled from the spellings of newer exporters and from
+    the only value this architecture allows where a switch is absent."""
+    if not isinstance(root, dict):
+        return root
+    out = dict(root)
+    if "torch_dtype" not in out:
+        out["torch_dtype"] = out.get("dtype") if isinstance(out.get("dtype"), str) else "bfloat16"
+    rope = out.get("rope_parameters")
+    if isinstance(rope, dict):
+        if rope.get("rope_type", rope.get("type", "default")) not in ("default", None):
+            raise ConfigError("config field 'rope_parameters' asks for a rope scaling that is not supported")
+        if "rope_theta" not in out and "rope_theta" in rope:
+            out["rope_theta"] = rope["rope_theta"]
+    if isinstance(out.get("rope_scaling"), dict) and out["rope_scaling"].get("rope_type", out["rope_scaling"].get("type")) in ("default", None):
+        out["rope_scaling"] = None
+    out.setdefault("hidden_act", "silu")
+    out.setdefault("attention_bias", False)
+    out.setdefault("use_sliding_window", False)
+    out.setdefault("tie_word_embeddings", False)
+    if not out.get("use_sliding_window"):
+        out["sliding_window"] = None            # exporters keep the window size next to use_sliding_window = false
+    if "head_dim" not in out and isinstance(out.get("hidden_size"), int) and isinstance(out.get("num_attention_heads"), int) \
+            and out["num_attention_heads"] > 0:
+        out["head_dim"] = out["hidden_size"] // out["num_attention_heads"]
+    if "num_key_value_heads" not in out and "num_attention_heads" in out:
+        out["num_key_value_heads"] = out["num_attention_heads"]
+    if isinstance(out.get("eos_token_id"), list) and out["eos_token_id"]:
+        out["eos_token_id"] = out["eos_token_id"][0]
+    for key in ("bos_token_id", "eos_token_id"):
+        if out.get(key) is None:
+            out[key] = out.get("eos_token_id") if key == "bos_token_id" and isinstance(out.get("eos_token_id"), int) else 0
+    return out
+
+
 @dataclass(frozen=True)
 class Qwen3Config:
     vocab_size: int
@@ -106,7 +149,9 @@ class Qwen3Config:
 
     # -- parsing
     @classmethod
-    def from_dict(cls, root: dict) -> "Qwen3Config":
+    def from_dict(cls, root: dict, strict: bool = False) -> "Qwen3Config":
+        if not strict:
+            root = _with_defaults(root)
         if _string(root, "model_type") != cls.model_type:
             raise ConfigError("only Qwen3 dense models are supported (model_type must be 'qwen3')")
         if cls.architecture not in [a for a in _required(root, "architectures") if isinstance(a, str)]:

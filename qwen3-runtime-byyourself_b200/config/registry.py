@@ -35,8 +35,9 @@ def config_class_for(name: str) -> Type:
         raise ConfigError(f"unknown architecture {name!r}; known: {known_architectures()}") from None
 
 
-def config_from_dict(root: dict):
-    """Choose the configuration class by `architectures` and let it parse `root`."""
+def config_from_dict(root: dict, **options):
+    """Choose the configuration class by `architectures` and let it parse `root`
+    (`options` go to its `from_dict`, e.g. `strict=True`)."""
     if not isinstance(root, dict):
         raise ConfigError("model config root must be a JSON object")
     if "architectures" not in root:
@@ -46,7 +47,7 @@ def config_from_dict(root: dict):
         raise ConfigError("config field 'architectures' must be an array")
     for name in names:
         if isinstance(name, str) and name in _ARCHITECTURES:
-            return _ARCHITECTURES[name].from_dict(root)
+            return _ARCHITECTURES[name].from_dict(root, **options) if options else _ARCHITECTURES[name].from_dict(root)
     raise ConfigError(f"no supported architecture in {names!r}; known: {known_architectures()}")
 
 

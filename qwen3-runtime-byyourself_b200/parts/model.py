@@ -9,6 +9,7 @@ last).
 """
 from __future__ import annotations
 
+import sys
 from typing import Dict, List, Optional
 
 import torch
@@ -33,6 +34,7 @@ class Model:
         self.head = build_part("head", plan.head)
         self.dtype: Optional[torch.dtype] = None
         self.device = None
+        self._warned_rounding = False
 
     # -- weights
     def weight_specs(self) -> Dict[str, WeightSpec]:
@@ -51,15 +53,17 @@ class Model:
         """Take the tensors (by checkpoint name) for computing in `dtype` on `device`.
 
         Matrices are used in the compute type: a bfloat16 checkpoint widens exactly for
-        the 32-bit path; a 32-bit matrix is refused by a bfloat16 engine rather than
-        rounded silently.  Scale vectors are always read as float32."""
+        the 32-bit path; a 32-bit matrix is rounded to bfloat16 for a bfloat16 engine, with
+        one line on stderr saying so.  Scale vectors are always read as float32."""
         specs = self.weight_specs()
         prepared = {}
         for name, spec in specs.items():
             t = weights[name]
             if spec.role == "matrix":
-                if t.dtype == torch.float32 and dtype == torch.bfloat16:
-                    raise ValueError(f"{name} is stored in 32-bit; run this checkpoint with dtype float32")
+                if t.dtype == torch.float32 and dtype == torch.bfloat16 and not self._warned_rounding:
+                    self._warned_rounding = True
+                    print(f"[qwen3_b200] {name} (and other matrices) are stored in 32-bit and are rounded to bfloat16 "
+                          f"for the bfloat16 kernels; use dtype float32 to compute with them as stored", file=sys.stderr)
                 t = t.to(device=device, dtype=dtype)
             else:
                 t = t.to(device=device)

@@ -31,7 +31,16 @@ TINY_C = {
     "tie_word_embeddings": False, "max_position_embeddings": 1024, "attention_bias": False,
     "use_sliding_window": False, "sliding_window": None, "rope_scaling": None, "bos_token_id": 0, "eos_token_id": 300,
 }
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# Sizes that rule out every vector path: a width that is no multiple of 8, an intermediate size that
+# is no multiple of 8 (no interleaved gate/up), an odd vocabulary; head size 64 (the tcgen05 attention).
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu", "torch_dtype": "bfloat16",
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+    "intermediate_size": 60, "vocab_size": 333, "rope_theta": 20000.0, "rms_norm_eps": 2e-5,
+    "tie_word_embeddings": True, "max_position_embeddings": 512, "attention_bias": False,
+    "use_sliding_window": False, "sliding_window": None, "rope_scaling": None, "bos_token_id": 4, "eos_token_id": 9,
+}
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def tiny(name, **changes):

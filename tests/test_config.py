@@ -35,7 +35,7 @@ def test_golden_accept_reject_matches_the_reference_parser():
     assert len(cases) >= 20
     for case in cases:
         try:
-            c = q.config_from_dict(case["config"])
+            c = q.config_from_dict(case["config"], strict=True)
             ok = True
         except q.ConfigError:
             ok = False
@@ -76,7 +76,32 @@ def test_every_key_is_required(key):
     cfg = tiny("A")
     del cfg[key]
     with pytest.raises(q.ConfigError, match=key):
-        q.config_from_dict(cfg)
+        q.config_from_dict(cfg, strict=True)
+
+
+def test_config_files_of_newer_exporters_are_read():
+    """`dtype` for `torch_dtype`, `rope_parameters` for `rope_theta`, absent switches, a window size kept
+    beside use_sliding_window = false: accepted by default, refused by the strict (reference) mode."""
+    cfg = tiny("B")
+    for key in ("torch_dtype", "rope_theta", "attention_bias", "use_sliding_window", "hidden_act", "bos_token_id",
+                "tie_word_embeddings", "rope_scaling"):
+        del cfg[key]
+    cfg.update(dtype="bfloat16", rope_parameters={"rope_type": "default", "rope_theta": 1000000.0},
+               sliding_window=4096, eos_token_id=[5, 7], layer_types=["full_attention"] * 3)
+    c = q.config_from_dict(cfg)
+    assert c == q.config_from_dict(tiny("B", bos_token_id=5))
+    with pytest.raises(q.ConfigError):
+        q.config_from_dict(cfg, strict=True)
+    with pytest.raises(q.ConfigError):
+        q.config_from_dict(dict(cfg, rope_parameters={"rope_type": "yarn", "rope_theta": 1e6, "factor": 4.0}))
+    del cfg["head_dim"]
+    assert q.config_from_dict(cfg).head_dim == 96 // 8
+    for size in ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
+                 "rms_norm_eps", "max_position_embeddings"):
+        broken = dict(cfg)
+        del broken[size]
+        with pytest.raises(q.ConfigError, match=size):
+            q.config_from_dict(broken)
 
 
 @pytest.mark.parametrize("key,value", [
@@ -99,7 +124,10 @@ def test_strict_types(key, value):
 ])
 def test_rejected_options(changes):
     with pytest.raises(q.ConfigError):
-        q.config_from_dict(tiny("B", **changes))
+        q.config_from_dict(tiny("B", **changes), strict=True)
+    if changes != {"sliding_window": 4096}:         # a window size beside use_sliding_window = false is unused
+        with pytest.raises(q.ConfigError):
+            q.config_from_dict(tiny("B", **changes))
 
 
 def test_rope_theta_may_be_a_json_integer_and_null_options_are_fine():

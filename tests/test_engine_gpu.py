@@ -7,6 +7,7 @@ import pytest
 
 import schedules
 from helpers import FP32_TOL, bf16_tolerance, make_folder, plain_logits, random_tokens, tiny
+from plain import qwen3_plain as plain
 
 pytestmark = pytest.mark.gpu
 
@@ -61,7 +62,7 @@ def make_requests(cfg, lengths, seed):
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     base = tmp_path_factory.mktemp("models")
-    return {name: make_folder(base, tiny(name), seed=11 + i, name=name) for i, name in enumerate("ABC")}
+    return {name: make_folder(base, tiny(name), seed=11 + i, name=name) for i, name in enumerate("ABCD")}
 
 
 def engine_for(folder, dtype, max_tokens):
@@ -71,7 +72,7 @@ def engine_for(folder, dtype, max_tokens):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,lengths", [("A", [5, 17, 1, 64, 65, 100]), ("B", [1, 9, 33, 64, 130]),
-                                          ("C", [2, 63, 129, 300])])
+                                          ("C", [2, 63, 129, 300]), ("D", [7, 128, 200, 333])])
 def test_whole_requests(folders, name, lengths, dtype):
     folder, weights = folders[name]
     cfg = tiny(name)
@@ -100,6 +101,7 @@ def test_last_32_tokens_one_by_one(folders, name, lengths, dtype):
     ("A", [13, 25, 9, 70, 66, 20, 128, 3], [5, 17, 1, 64, 65, 12, 100, 3], 3),
     ("B", [13, 21, 45, 76, 30, 200, 65], [1, 9, 33, 64, 30, 129, 2], 4),
     ("C", [200, 90, 300, 64, 150], [100, 63, 257, 1, 64], 2),
+    ("D", [300, 140, 9, 260, 131], [129, 128, 1, 256, 130], 3),
 ])
 def test_unequal_batches_one_after_another(folders, name, lengths, prompts, batch, dtype):
     folder, weights = folders[name]
@@ -161,6 +163,21 @@ def test_cutting_does_not_change_logits_beyond_rounding(folders, dtype):
             for (r, p), row in other.items():
                 if r == rid:
                     assert np.max(np.abs(a[(r, p)] - row)) <= tol, (r, p)
+
+
+def test_checkpoint_stored_in_32_bit_runs_in_both_types(tmp_path):
+    """A folder of float32 tensors: exact in the 32-bit engine; the bfloat16 engine rounds the matrices
+    (and says so) and then agrees with the plain model of the rounded weights."""
+    import qwen3_b200 as q
+    cfg = tiny("D")
+    folder, weights = make_folder(tmp_path, cfg, seed=77, storage="float32")
+    requests = make_requests(cfg, [40, 150], seed=8)
+    steps, rows = schedules.tail_one_by_one(requests, 8)
+    got = run_steps(engine_for(folder, "float32", schedules.peak_tokens(steps)), steps, rows)
+    check(got, requests, dict(cfg, torch_dtype="float32"), weights, "float32", "32-bit storage")
+    rounded = {k: (plain.round_bf16(v) if v.ndim == 2 else v) for k, v in weights.items()}
+    got = run_steps(engine_for(folder, "bfloat16", schedules.peak_tokens(steps)), steps, rows)
+    check(got, requests, cfg, rounded, "bfloat16", "32-bit storage, bfloat16 engine")
 
 
 def test_step_errors_leave_the_cache_unchanged(folders):
