@@ -228,3 +228,97 @@ def test_layer_order_is_data_and_a_layer_can_read_another_layers_cache(tmp_path)
     engine.step([q.StepEntry(s, [5, 6, 7], [])])
     b = engine.step([q.StepEntry(s, [8], [0])]).cpu().numpy()
     assert np.all(np.isfinite(a)) and np.max(np.abs(a - b)) <= 2e-5
+
+
+def windowed_plain_forward(cfg, w, tokens, window_layers, window):
+    """The plain model with a window on the attention of some layers."""
+    x = plain.embedding(tokens, w["model.embed_tokens.weight"])
+    T = len(tokens)
+    cos, sin = plain.rope_table(T, cfg["head_dim"], cfg["rope_theta"])
+    nq, nkv, d, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    pos = np.arange(T)
+    for layer in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{layer}."
+        a = plain.rms_norm(x, w[p + "input_layernorm.weight"], eps)
+        qh = plain.linear(a, w[p + "self_attn.q_proj.weight"]).reshape(T, nq, d)
+        kh = plain.linear(a, w[p + "self_attn.k_proj.weight"]).reshape(T, nkv, d)
+        vh = plain.linear(a, w[p + "self_attn.v_proj.weight"]).reshape(T, nkv, d)
+        qh = plain.apply_rope(plain.rms_norm(qh, w[p + "self_attn.q_norm.weight"], eps), pos, cos, sin)
+        kh = plain.apply_rope(plain.rms_norm(kh, w[p + "self_attn.k_norm.weight"], eps), pos, cos, sin)
+        ctx = plain.gqa_attention(qh, kh, vh, window=window if layer in window_layers else None).reshape(T, nq * d)
+        x = x + plain.linear(ctx, w[p + "self_attn.o_proj.weight"])
+        m = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
+        x = x + plain.mlp(m, w, p)
+    x = plain.rms_norm(x, w["model.norm.weight"], eps)
+    return plain.linear(x, plain.output_weight(cfg, w))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_window_layers_have_pages_of_their_own_and_give_them_back(dtype):
+    """Layers 0 and 2 keep every key, layer 1 a window of 70: two cache groups.  Whole prompts, token by
+    token and unequal batches agree with the plain windowed model, and the window group returns the pages
+    that fell out of the window while the sequences are still running."""
+    import qwen3_b200 as q
+    from qwen3_b200.engine.engine import Engine
+    from test_engine_gpu import run_steps
+    cfg = tiny("B")
+    config = q.config_from_dict(cfg)
+    plan = config.plan()
+    windowed = dataclasses.replace(plan.layers[1], mixer=q.PartSpec("gqa_attention", dict(plan.layers[1].mixer.params, window=70)))
+    plan = dataclasses.replace(plan, layers=[plan.layers[0], windowed, plan.layers[2]])
+    model = q.build_model(plan)
+    tensors = q.random_weights(model.weight_specs(), seed=12, dtype=torch.bfloat16)
+    weights = {k: v.double().numpy() for k, v in tensors.items()}
+    model.bind(dict(tensors), dtype, "cuda")
+    rng = np.random.default_rng(4)
+    requests = {f"r{i}": [int(t) for t in rng.integers(0, cfg["vocab_size"], n)] for i, n in enumerate([250, 60, 139, 200])}
+    tol_f32 = 1e-4
+    for builder in (schedules.whole, lambda r: schedules.tail_one_by_one(r, 32),
+                    lambda r: schedules.batched(r, {"r0": 100, "r1": 1, "r2": 139, "r3": 64}, 2)):
+        steps, rows = builder(requests)
+        engine = Engine(model, config, max_tokens=schedules.peak_tokens(steps))
+        assert [g.need.kind for g in engine.cache.groups] == ["full", "window"]
+        assert [g.layers for g in engine.cache.groups] == [[0, 2], [1]]
+        got = run_steps(engine, steps, rows)
+        for rid, toks in requests.items():
+            want = windowed_plain_forward(cfg, weights, toks, {1}, 70)
+            if dtype == torch.float32:
+                tol = tol_f32
+            else:
+                tol = 4.0 * float(np.max(np.abs(want - windowed_plain_forward_bf16(cfg, weights, toks, {1}, 70)))) + 1e-6
+            for p in range(len(toks)):
+                if (rid, p) in got:
+                    err = float(np.max(np.abs(got[(rid, p)] - want[p])))
+                    assert err <= tol, (rid, p, err, tol)
+    # a running sequence of 250 tokens holds 4 pages of full keys but only the window's pages in the other group
+    engine = Engine(model, config, max_tokens=256)
+    s = engine.new_sequence()
+    engine.step([q.StepEntry(s, requests["r0"], [])])
+    full, window = engine.cache.groups
+    assert len(full.held_pages(s)) == 4 and len(window.held_pages(s)) == 2
+    engine.release(s)
+    assert full.n_free == full.n_pages and window.n_free == window.n_pages
+
+
+def windowed_plain_forward_bf16(cfg, w, tokens, window_layers, window):
+    """The same with bfloat16 rounding at the reference's rounding points (the yardstick of the bfloat16 run)."""
+    rnd = plain.round_bf16
+    x = plain.embedding(tokens, w["model.embed_tokens.weight"])
+    T = len(tokens)
+    cos, sin = plain.rope_table(T, cfg["head_dim"], cfg["rope_theta"])
+    nq, nkv, d, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    pos = np.arange(T)
+    for layer in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{layer}."
+        a = plain.rms_norm(x, w[p + "input_layernorm.weight"], eps, rnd)
+        qh = plain.linear(a, w[p + "self_attn.q_proj.weight"], rnd).reshape(T, nq, d)
+        kh = plain.linear(a, w[p + "self_attn.k_proj.weight"], rnd).reshape(T, nkv, d)
+        vh = plain.linear(a, w[p + "self_attn.v_proj.weight"], rnd).reshape(T, nkv, d)
+        qh = plain.apply_rope(plain.rms_norm(qh, w[p + "self_attn.q_norm.weight"], eps, rnd), pos, cos, sin, rnd)
+        kh = plain.apply_rope(plain.rms_norm(kh, w[p + "self_attn.k_norm.weight"], eps, rnd), pos, cos, sin, rnd)
+        ctx = plain.gqa_attention(qh, kh, vh, rnd, window=window if layer in window_layers else None).reshape(T, nq * d)
+        x = rnd(x + plain.linear(ctx, w[p + "self_attn.o_proj.weight"], rnd))
+        m = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], eps, rnd)
+        x = rnd(x + plain.mlp(m, w, p, rnd))
+    x = plain.rms_norm(x, w["model.norm.weight"], eps, rnd)
+    return plain.linear(x, plain.output_weight(cfg, w))
