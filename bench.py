@@ -1,7 +1,7 @@
 """Benchmark of the library's headline metric: decoded tokens a second of a Qwen3-8B-shaped
 model with random weights in bfloat16 on one B200, batch 8 at a context of 4,096 tokens.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 8b|14b|32b]
 
 Prints ONE JSON line.  A "step" is one decode step of the whole batch.
   value     decoded tokens a second, timed on the device with CUDA events around K steps;
@@ -13,6 +13,8 @@ Prints ONE JSON line.  A "step" is one decode step of the whole batch.
   roofline  bytes a decode step has to read (every weight it uses once, and the cache of the
             live requests) over its time, against the measured copy bandwidth
   points    decoded tokens a second at batch 1 and batch 64 (unequal prompts up to 2,048)
+`--shape 14b` and `--shape 32b` run the same measurement on the two larger shapes of the baseline's
+list (context 8,192 at batch 16; context 16,384 at batch 8), without the batch-1/64 points.
 Peaks are read from MEASURED_PEAKS.json beside this file if it exists, else the stated
 fallback of an earlier measurement on the same pool is used.
 """
@@ -39,7 +41,12 @@ QWEN3_8B = {
     "attention_bias": False, "use_sliding_window": False, "sliding_window": None, "rope_scaling": None,
     "bos_token_id": 151643, "eos_token_id": 151645,
 }
-CONTEXT = 4096
+# the further shapes of the baseline's list: (layers, hidden, q heads, intermediate), context, batch
+SHAPES = {
+    "8b": (dict(QWEN3_8B), 4096, 8),
+    "14b": (dict(QWEN3_8B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408), 8192, 16),
+    "32b": (dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600), 16384, 8),
+}
 PREFILL_TOKENS = 2048
 
 
@@ -192,7 +199,9 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (both are reported)")
-    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="model shape; 8b is the headline")
+    ap.add_argument("--batch", type=int, default=None, help="default: the shape's own (8b: 8, 14b: 16, 32b: 8)")
+    ap.add_argument("--context", type=int, default=None, help="default: the shape's own (8b: 4096, 14b: 8192, 32b: 16384)")
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
     args = ap.parse_args()
 
@@ -211,14 +220,15 @@ def main() -> int:
     import qwen3_b200 as q
     from qwen3_b200.sampling.sampler import Sampler
 
-    cfg = dict(QWEN3_8B)
+    cfg, CONTEXT, shape_batch = SHAPES[args.shape]
+    CONTEXT = args.context or CONTEXT
     layers = args.layers or cfg["num_hidden_layers"]
     config = q.config_from_dict(dict(cfg, num_hidden_layers=layers))
     peaks = load_peaks()
     rng = np.random.default_rng(0)
     torch.cuda.set_device(0)
-    batch = args.batch
-    max_batch = batch if args.skip_points else max(batch, 64)
+    batch = args.batch or shape_batch
+    max_batch = batch if (args.skip_points or args.shape != "8b") else max(batch, 64)
     engine = q.Engine.from_random(config, seed=0, dtype="bfloat16", max_tokens=max_batch * CONTEXT,
                                   max_seq_len=CONTEXT)
     sampler = Sampler(q.SamplingParams(mode="greedy"), engine.vocab_size, engine.device)
@@ -232,7 +242,7 @@ def main() -> int:
     h2d = engine.last_upload_bytes
 
     points = {}
-    if not args.skip_points:
+    if not args.skip_points and args.shape == "8b":
         for b in (1, 64):
             r = decode_run(q, engine, sampler, torch, rng, b, 2048, min(args.steps, 32), warmup)
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
@@ -255,16 +265,16 @@ def main() -> int:
     flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
 
     line = {
-        "metric": "decode tok/s at batch 8, context 4096 (Qwen3-8B shape, random weights, 1 B200)",
+        "metric": f"decode tok/s at batch {batch}, context {CONTEXT} (Qwen3-{args.shape.upper()} shape, random weights, 1 B200)",
         "value": round(head["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(head["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights, uniform-random token ids", "impl": "ours",
-        "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_of_config": cfg["num_hidden_layers"],
+        "config": {"model": f"Qwen3-{args.shape.upper()} shape", "layers": layers, "layers_of_config": cfg["num_hidden_layers"],
                    "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": batch,
                    "seq_len": CONTEXT, "longest_context_reached": head["longest"], "parallelism": "none (1 GPU)",
-                   "cache": "paged, 64 tokens a page", "l2": "a step reads >15 GB of weights, far above the 126 MB L2",
+                   "cache": "paged, 64 tokens a page", "l2": "a step reads every weight (GBs), far above the 126 MB L2",
                    "sampling": "greedy on the device"},
         "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms"], 4),
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4 * batch},

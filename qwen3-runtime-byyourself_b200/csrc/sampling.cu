@@ -57,11 +57,23 @@ argmax_kernel(const float* __restrict__ logits, int64_t stride, int valid, int* 
     const float* x = logits + (int64_t)blockIdx.x * stride;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < valid; i += THREADS) {
-        float v = x[i];
+    auto take = [&](float v, int i) {
         if (isnan(v)) v = -INFINITY;
         if (v > bv || bi == 0x7fffffff) { bv = v; bi = i; }
+    };
+    // a thread sees its indices in ascending order, so "greater, or the first" keeps the lowest id
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+        const int n4 = valid >> 2;
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+#pragma unroll 4
+        for (int i = threadIdx.x; i < n4; i += THREADS) {
+            const float4 v = x4[i];
+            take(v.x, 4 * i); take(v.y, 4 * i + 1); take(v.z, 4 * i + 2); take(v.w, 4 * i + 3);
+        }
+        done = n4 << 2;
     }
+    for (int i = done + threadIdx.x; i < valid; i += THREADS) take(x[i], i);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);

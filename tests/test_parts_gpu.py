@@ -322,3 +322,146 @@ def windowed_plain_forward_bf16(cfg, w, tokens, window_layers, window):
         x = rnd(x + plain.mlp(m, w, p, rnd))
     x = plain.rms_norm(x, w["model.norm.weight"], eps, rnd)
     return plain.linear(x, plain.output_weight(cfg, w))
+
+
+# ------------------------------------------------------- a toy routed feed-forward and a toy position encoding
+class TopOneExperts:
+    """out = p_e . W2_e relu(W1_e x), e = the expert with the largest router logit, p_e its softmax weight.
+    Written against the documented feed-forward interface; device-only arithmetic (every expert is computed
+    and the others are masked away), so that it is safe inside a captured step."""
+
+    def __init__(self, hidden_size, inner_size, n_experts, prefix="moe."):
+        self.H, self.I, self.E, self.prefix = hidden_size, inner_size, n_experts, prefix
+
+    def weight_specs(self, prefix):
+        from qwen3_b200 import WeightSpec
+        p = prefix + self.prefix
+        specs = {p + "router.weight": WeightSpec((self.E, self.H))}
+        for e in range(self.E):
+            specs[p + f"experts.{e}.w1.weight"] = WeightSpec((self.I, self.H))
+            specs[p + f"experts.{e}.w2.weight"] = WeightSpec((self.H, self.I))
+        return specs
+
+    def bind(self, weights, prefix, dtype, device):
+        p = prefix + self.prefix
+        self.router = weights.pop(p + "router.weight").float()
+        self.w1 = torch.stack([weights.pop(p + f"experts.{e}.w1.weight") for e in range(self.E)]).float()
+        self.w2 = torch.stack([weights.pop(p + f"experts.{e}.w2.weight") for e in range(self.E)]).float()
+
+    def forward(self, x, ctx):
+        xf = x.float()
+        logits = xf @ self.router.t()                                     # router in 32-bit
+        prob = torch.softmax(logits, dim=-1)
+        chosen = torch.nn.functional.one_hot(torch.argmax(logits, dim=-1), self.E).float()
+        inner = torch.relu(torch.einsum("eih,nh->eni", self.w1, xf))
+        each = torch.einsum("ehi,eni->enh", self.w2, inner)              # [E, N, H]
+        out = ctx.scratch.get("toy.moe_out", (ctx.n_tokens, self.H), ctx.dtype)
+        out.copy_(torch.einsum("enh,ne->nh", each, chosen * prob))
+        return out
+
+
+class PairwiseLinearRotation:
+    """Rotates the adjacent pairs (x[2j], x[2j+1]) by position . (j + 1) . step: another position encoding
+    than the library's, without kernel tables, so that the mixer takes its unfused way."""
+
+    def __init__(self, head_dim, step):
+        self.head_dim, self.step, self.table = head_dim, step, None
+
+    def prepare(self, n_positions, device):
+        if self.table is None or self.table.shape[1] < n_positions:
+            angle = torch.arange(n_positions, dtype=torch.float64)[:, None] * \
+                (torch.arange(1, self.head_dim // 2 + 1, dtype=torch.float64) * self.step)[None, :]
+            self.table = torch.stack([torch.cos(angle), torch.sin(angle)]).float().to(device)
+
+    def apply_(self, q, k, positions):
+        cos, sin = self.table[0][positions.long()][:, None, :], self.table[1][positions.long()][:, None, :]
+        for t in (q, k):
+            a, b = t[..., 0::2].float(), t[..., 1::2].float()
+            ra, rb = a * cos - b * sin, a * sin + b * cos
+            t[..., 0::2], t[..., 1::2] = ra.to(t.dtype), rb.to(t.dtype)
+
+
+def toy_parts_plain_forward(cfg, w, tokens, step, n_experts):
+    """Layer 0 with the pairwise rotation, layer 1 with the routed feed-forward, layer 2 as the model has it."""
+    x = plain.embedding(tokens, w["model.embed_tokens.weight"])
+    T = len(tokens)
+    cos, sin = plain.rope_table(T, cfg["head_dim"], cfg["rope_theta"])
+    nq, nkv, d, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    angle = np.arange(T)[:, None] * (np.arange(1, d // 2 + 1) * step)[None, :]
+    c32, s32 = np.cos(angle).astype(np.float32).astype(np.float64)[:, None, :], np.sin(angle).astype(np.float32).astype(np.float64)[:, None, :]
+
+    def rotate(t):
+        a, b = t[..., 0::2], t[..., 1::2]
+        out = np.empty_like(t)
+        out[..., 0::2], out[..., 1::2] = a * c32 - b * s32, a * s32 + b * c32
+        return out
+
+    for layer in range(3):
+        p = f"model.layers.{layer}."
+        if layer == 0:
+            a = plain.rms_norm(x, w[p + "input_layernorm.weight"], eps)
+            qh = plain.linear(a, w[p + "self_attn.q_proj.weight"]).reshape(T, nq, d)
+            kh = plain.linear(a, w[p + "self_attn.k_proj.weight"]).reshape(T, nkv, d)
+            vh = plain.linear(a, w[p + "self_attn.v_proj.weight"]).reshape(T, nkv, d)
+            qh = rotate(plain.rms_norm(qh, w[p + "self_attn.q_norm.weight"], eps))
+            kh = rotate(plain.rms_norm(kh, w[p + "self_attn.k_norm.weight"], eps))
+            x = x + plain.linear(plain.gqa_attention(qh, kh, vh).reshape(T, nq * d), w[p + "self_attn.o_proj.weight"])
+            m = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
+            x = x + plain.mlp(m, w, p)
+        elif layer == 1:
+            a = plain.rms_norm(x, w[p + "input_layernorm.weight"], eps)
+            x = x + plain.self_attention(a, np.arange(T), cfg, w, p, cos, sin)
+            m = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
+            logits = m @ w[p + "moe.router.weight"].T
+            e = np.argmax(logits, axis=-1)
+            prob = np.exp(logits - logits.max(-1, keepdims=True))
+            prob = prob / prob.sum(-1, keepdims=True)
+            out = np.zeros_like(m)
+            for t in range(T):
+                inner = np.maximum(w[p + f"moe.experts.{e[t]}.w1.weight"] @ m[t], 0.0)
+                out[t] = prob[t, e[t]] * (w[p + f"moe.experts.{e[t]}.w2.weight"] @ inner)
+            x = x + out
+        else:
+            x = plain.decoder_layer(x, np.arange(T), cfg, w, layer, cos, sin)
+    x = plain.rms_norm(x, w["model.norm.weight"], eps)
+    return plain.linear(x, plain.output_weight(cfg, w))
+
+
+def test_toy_routed_feed_forward_and_toy_position_encoding():
+    """A feed-forward with routing in layer 1 and another position encoding in layer 0, both defined here and
+    registered from here: the model builds from the plan and steps whole, token by token and in unequal
+    batches (decode steps captured) in agreement with the plain restatement, in 32-bit."""
+    import qwen3_b200 as q
+    from qwen3_b200.engine.engine import Engine
+    from test_engine_gpu import run_steps
+    q.register_part("feed_forward", "top1_experts", TopOneExperts)
+    q.register_part("position", "pairwise_linear", PairwiseLinearRotation)
+    cfg = tiny("B")
+    config = q.config_from_dict(cfg)
+    plan = config.plan()
+    H, d, E, step = cfg["hidden_size"], cfg["head_dim"], 3, 0.013
+    layer0 = dataclasses.replace(plan.layers[0], mixer=q.PartSpec("gqa_attention", dict(
+        plan.layers[0].mixer.params, position=q.PartSpec("pairwise_linear", {"head_dim": d, "step": step}))))
+    layer1 = dataclasses.replace(plan.layers[1], feed_forward=q.PartSpec("top1_experts", {
+        "hidden_size": H, "inner_size": 40, "n_experts": E}))
+    plan = dataclasses.replace(plan, layers=[layer0, layer1, plan.layers[2]])
+    model = q.build_model(plan)
+    specs = model.weight_specs()
+    assert "model.layers.1.moe.router.weight" in specs and "model.layers.1.mlp.gate_proj.weight" not in specs
+    tensors = q.random_weights(specs, seed=8, dtype=torch.float32)
+    # random routers barely prefer an expert: widen them so that choices are clear of rounding
+    tensors["model.layers.1.moe.router.weight"] = tensors["model.layers.1.moe.router.weight"] * 40.0
+    weights = {k: v.double().numpy() for k, v in tensors.items()}
+    model.bind(dict(tensors), torch.float32, "cuda")
+    rng = np.random.default_rng(6)
+    requests = {f"r{i}": [int(t) for t in rng.integers(0, cfg["vocab_size"], n)] for i, n in enumerate([70, 9, 130, 41])}
+    for builder in (schedules.whole, lambda r: schedules.tail_one_by_one(r, 32),
+                    lambda r: schedules.batched(r, {"r0": 6, "r1": 9, "r2": 64, "r3": 1}, 2)):
+        steps, rows = builder(requests)
+        engine = Engine(model, config, max_tokens=schedules.peak_tokens(steps))
+        got = run_steps(engine, steps, rows)
+        for rid, toks in requests.items():
+            want = toy_parts_plain_forward(cfg, weights, toks, step, E)
+            for p in range(len(toks)):
+                if (rid, p) in got:
+                    assert np.max(np.abs(got[(rid, p)] - want[p])) <= 1e-4, (rid, p)
