@@ -1,21 +1,29 @@
-// Blackwell matrix product for the projections: Y[M,N] = X[M,K] . W[N,K]^T, bfloat16
-// operands, 32-bit accumulation in tensor memory, bfloat16 or float32 output.
+// Blackwell matrix products for the projections: Y[M,N] = X[M,K] . W[N,K]^T, bfloat16
+// operands, 32-bit accumulation in tensor memory, bfloat16 or float32 output.  They replace
+// the reference's cublasGemmEx call per projection (src/ops/linear.cpp:165-193).
 //
-// It replaces the reference's cublasGemmEx call per projection (src/ops/linear.cpp:165-193).
-// The tile is computed "weights first": D[128 rows of W, BN tokens] = W_tile . X_tile^T, so
-// the 128-row operand of tcgen05.mma is always full whatever the number of tokens, and the
-// same kernel serves prompts (BN = 128 or 256 tokens per tile) and decode steps (BN = 16..64,
-// K split over blockIdx.z with float32 partial tiles).
+// Two forms share the building blocks (TMA loads of 128-byte-swizzled K-major tiles into a
+// ring of shared-memory stages, tcgen05.mma issued by one thread, accumulator in tensor
+// memory, tcgen05.ld epilogue):
 //
-// One tile per block; three roles:
-//   warp 0     TMA producer: cp.async.bulk.tensor loads of the W and X tiles (128-byte
-//              swizzle, K-major) into a ring of shared-memory stages, signalled by mbarriers
-//   warp 1     allocates tensor memory; one thread issues tcgen05.mma (M=128, N=BN, K=16,
+//   * the "weights first" form for 17..128 rows (large decode batches, short prompts), where
+//     the product is bound by reading W once: D[128 rows of W, MT tokens] = W_tile . X_tile^T,
+//     so the 128-row operand of the instruction is full whatever the number of tokens.  When W
+//     has few rows, K is split over the blocks of a thread-block cluster; their partial tiles
+//     meet in shared memory (each block reduces a share of the tokens over distributed shared
+//     memory, in block order) and one kernel writes the finished output.
+//   * the "tokens first" persistent form for prompts, further down.
+//
+// Roles in a block of the first form:
+//   warp 0     TMA producer
+//   warp 1     allocates tensor memory; one thread issues tcgen05.mma (M=128, N=MT, K=16,
 //              four per stage) and commits each stage back to the producer
-//   warps 2-5  epilogue: tcgen05.ld of the accumulator (one TMEM lane = one row of W per
-//              thread), conversion, and stores Y[token][row] that are contiguous over a warp
+//   warps 2-5  drain the accumulator (one TMEM lane = one row of W per thread) into shared memory
+//   all        after the cluster barrier: reduce over the cluster, convert, store (optionally
+//              SiLU(gate) * up of interleaved rows)
 // Every wait on an mbarrier is bounded: after Q3_WAIT_LIMIT polls the thread records where it
-// gave up in `status` and the block winds down (tensor memory is freed on every path).
+// gave up in `status` and the block winds down (tensor memory is freed on every path, and the
+// cluster barriers are reached by every thread on every path).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -94,32 +102,71 @@ template <typename OutT> __device__ __forceinline__ OutT to_out(float v);
 template <> __device__ __forceinline__ float to_out<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 to_out<bf16>(float v) { return __float2bfloat16_rn(v); }
 
-template <int BN, int STAGES> struct Smem {
-    static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;          // both multiples of 1024
-    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
-};
+// ---- thread-block cluster helpers
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The address of `addr` (a shared-memory address of this block) in the block of rank `rank`.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
+}
 
-// Y is [splits, M, N] when gridDim.z > 1 (float32 partial sums), else [M, N].
-template <int BN, int STAGES, typename OutT>
-__global__ void __launch_bounds__(THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                    OutT* __restrict__ Y, int M, int N, int K, int* __restrict__ status) {
+constexpr int PART_LD = BM + 4;         // floats per token in the partial tile (rows stay 16-byte aligned)
+
+template <typename OutT> __device__ __forceinline__ void store4(OutT* p, float4 v, bool vec, int valid);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v, bool vec, int valid) {
+    if (vec && valid >= 4) { *reinterpret_cast<float4*>(p) = v; return; }
+    const float e[4] = {v.x, v.y, v.z, v.w};
+    for (int i = 0; i < 4 && i < valid; ++i) p[i] = e[i];
+}
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float4 v, bool vec, int valid) {
+    if (vec && valid >= 4) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        return;
+    }
+    const float e[4] = {v.x, v.y, v.z, v.w};
+    for (int i = 0; i < 4 && i < valid; ++i) p[i] = __float2bfloat16_rn(e[i]);
+}
+
+// Grid (tiles of 128 rows of W, K ranges); the blocks of one tile form a cluster (1, gridDim.y, 1).
+// GATED: W holds gate and up rows interleaved in blocks of eight and Y is [M, N/2] = round(silu(g)) * u.
+template <int MT, int STAGES, int MINB, bool GATED, typename OutT>
+__global__ void __launch_bounds__(THREADS, MINB)
+gemm_tcgen05_mid_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                        OutT* __restrict__ Y, int M, int N, int K, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
-    using S = Smem<BN, STAGES>;
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = MT * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // multiples of 1024
+    constexpr uint32_t TMEM_COLS = MT < 32 ? 32 : MT;
+    static_assert(MT % 16 == 0 && MT >= 16 && MT <= 256, "token tile: the N of an M=128 tcgen05.mma");
+    static_assert(MT * PART_LD * 4 <= STAGES * STAGE_BYTES, "the partial tile reuses the stages");
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;         // 128-byte swizzle wants 1024-byte tiles
-    const uint32_t bars = base + STAGES * S::STAGE_BYTES;                 // full[STAGES], empty[STAGES], done, tmem slot
+    const uint32_t bars = base + STAGES * STAGE_BYTES;                    // full[STAGES], empty[STAGES], done, tmem slot
     const uint32_t bar_done = bars + 2 * STAGES * 8, tmem_slot = bar_done + 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN;
+    const int n0 = blockIdx.x * BM;
+    const uint32_t rank = cluster_rank(), ranks = gridDim.y;
     const int nkb_all = (K + BK - 1) / BK;
-    const int kb_begin = (int)(((int64_t)blockIdx.z * nkb_all) / gridDim.z);
-    const int kb_end = (int)(((int64_t)(blockIdx.z + 1) * nkb_all) / gridDim.z);
+    const int kb_begin = (int)(((int64_t)rank * nkb_all) / ranks);
+    const int kb_end = (int)(((int64_t)(rank + 1) * nkb_all) / ranks);
     const int nkb = kb_end - kb_begin;
 
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bars + s * 8, 1);
             mbar_init(bars + (STAGES + s) * 8, 1);
@@ -127,44 +174,51 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         mbar_init(bar_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
     __syncthreads();
-    tc_fence_after();
-    uint32_t tmem_base;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+    // the producer starts its stream now; tensor memory is handed out meanwhile and its address goes to
+    // the warps that use it over a barrier of their own (warps 1..5)
+    uint32_t tmem_base = 0;
+    if (warp >= 1) {
+        if (warp == 1) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
+        tc_fence_before();
+        asm volatile("bar.sync 1, %0;" ::"n"(THREADS - 32) : "memory");
+        tc_fence_after();
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+    }
 
     if (warp == 0) {
         // ---------------- producer
         if (lane == 0) {
-            bool ok = true;
-            for (int i = 0; i < nkb && ok; ++i) {
+            for (int i = 0; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
-                ok = mbar_wait(bars + (STAGES + s) * 8, phase ^ 1u);         // the stage is free
-                if (!ok) { atomicExch(status, 1); break; }
-                const uint32_t a = base + s * S::STAGE_BYTES, b = a + S::A_BYTES;
-                mbar_expect_tx(bars + s * 8, S::STAGE_BYTES);
+                if (!mbar_wait(bars + (STAGES + s) * 8, phase ^ 1u)) {      // the stage is free
+                    atomicExch(status, 1);
+                    break;
+                }
+                const uint32_t a = base + s * STAGE_BYTES, b = a + A_BYTES;
+                mbar_expect_tx(bars + s * 8, STAGE_BYTES);
                 tma_load_2d(a, &map_w, bars + s * 8, (kb_begin + i) * BK, n0);      // weights: independent of the
                 if (i == 0) pdl_wait();                                              // kernel before; X is not
-                tma_load_2d(b, &map_x, bars + s * 8, (kb_begin + i) * BK, m0);
+                tma_load_2d(b, &map_x, bars + s * 8, (kb_begin + i) * BK, 0);
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(BN);
-            bool ok = true;
-            for (int i = 0; i < nkb && ok; ++i) {
+            constexpr uint32_t idesc = make_idesc(MT);
+            for (int i = 0; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
-                ok = mbar_wait(bars + s * 8, phase);                         // the tiles have landed
-                if (!ok) { atomicExch(status, 2); break; }
+                if (!mbar_wait(bars + s * 8, phase)) {                       // the tiles have landed
+                    atomicExch(status, 2);
+                    break;
+                }
                 tc_fence_after();
-                const uint32_t a = base + s * S::STAGE_BYTES, b = a + S::A_BYTES;
+                const uint32_t a = base + s * STAGE_BYTES, b = a + A_BYTES;
                 const uint64_t da = make_desc(a), db = make_desc(b);
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k)                        // 32 bytes further along K per step
@@ -174,35 +228,74 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             tc_commit(bar_done);                                             // accumulator complete (or abandoned)
         }
     } else {
-        // ---------------- epilogue: warps 2..5 own TMEM lanes 32*(warp % 4) ..
-        const bool ok = mbar_wait(bar_done, 0);
-        if (!ok && lane == 0) atomicExch(status, 3);
+        // ---------------- warps 2..5 own TMEM lanes 32*(warp % 4) ..: accumulator -> part[token][row of W]
+        const bool ok = mbar_wait(bar_done, 0);                              // every load has landed and been consumed,
+        if (!ok && lane == 0) atomicExch(status, 3);                         // so the stages may be overwritten
         tc_fence_after();
-        pdl_wait();                                                          // no global write before this
-        if (ok && nkb > 0) {
-            const int lane_base = (warp & 3) * 32;
-            const int n = n0 + lane_base + lane;
-            OutT* y = Y + (int64_t)blockIdx.z * M * N;
+        float* part = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
+        const int lane_base = (warp & 3) * 32;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                uint32_t r[16];
+        for (int c = 0; c < MT; c += 16) {
+            uint32_t r[16];
+            if (ok && nkb > 0) {
                 tc_ld16(tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)c, r);
                 tc_wait_ld();
+            } else {                                                          // an empty K range adds nothing
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int m = m0 + c + j;
-                    if (m < M && n < N) y[(int64_t)m * N + n] = to_out<OutT>(__uint_as_float(r[j]));
-                }
+                for (int j = 0; j < 16; ++j) r[j] = 0u;
             }
-        } else if (ok) {                                                      // an empty K range adds nothing
-            const int n = n0 + (warp & 3) * 32 + lane;
-            OutT* y = Y + (int64_t)blockIdx.z * M * N;
-            for (int j = 0; j < BN; ++j)
-                if (m0 + j < M && n < N) y[(int64_t)(m0 + j) * N + n] = to_out<OutT>(0.0f);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) part[(c + j) * PART_LD + lane_base + lane] = __uint_as_float(r[j]);
         }
     }
     tc_fence_before();
-    __syncthreads();
+    __syncwarp();
+    cluster_sync();                                                           // every block's partial tile is in place
+
+    // ---------------- reduce over the cluster: this block finishes the tokens m with m % ranks == rank
+    pdl_wait();                                                               // no global write before this
+    {
+        const int out_n = GATED ? (N >> 1) : N;
+        const bool vec = (out_n % 4 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15u) == 0);
+        constexpr int GROUPS = GATED ? 16 : 32;                               // groups of four outputs per token and tile
+        const int my_tokens = (MT - (int)rank + (int)ranks - 1) / (int)ranks;
+        for (int idx = threadIdx.x; idx < my_tokens * GROUPS; idx += THREADS) {
+            const int m = (idx / GROUPS) * (int)ranks + (int)rank, g = idx % GROUPS;
+            if (m >= M) continue;
+            if constexpr (!GATED) {
+                const uint32_t addr = base + (uint32_t)(m * PART_LD + 4 * g) * 4u;
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (uint32_t s = 0; s < ranks; ++s) {
+                    const float4 v = ld_cluster_f4(map_to_rank(addr, s));
+                    sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+                }
+                const int n = n0 + 4 * g;
+                if (n < N) store4<OutT>(Y + (int64_t)m * N + n, sum, vec, N - n);
+            } else {
+                // rows 16t + 4h .. +3 are gates, rows 16t + 8 + 4h .. +3 the ups of features 8t + 4h .. +3
+                const int t = g >> 1, h = g & 1;
+                const uint32_t addr_g = base + (uint32_t)(m * PART_LD + 16 * t + 4 * h) * 4u, addr_u = addr_g + 32u;
+                float4 gs = make_float4(0.f, 0.f, 0.f, 0.f), us = gs;
+                for (uint32_t s = 0; s < ranks; ++s) {
+                    const float4 a = ld_cluster_f4(map_to_rank(addr_g, s)), b = ld_cluster_f4(map_to_rank(addr_u, s));
+                    gs.x += a.x; gs.y += a.y; gs.z += a.z; gs.w += a.w;
+                    us.x += b.x; us.y += b.y; us.z += b.z; us.w += b.w;
+                }
+                // both sums are rounded to bfloat16 as the two separate products of the reference would be,
+                // then round(silu(g)) * u (src/ops/elementwise.cu:47-65)
+                auto gate = [](float gv, float uv) {
+                    gv = round_to<bf16>(gv);
+                    uv = round_to<bf16>(uv);
+                    return round_to<bf16>(gv / (1.0f + expf(-gv))) * uv;
+                };
+                const float4 o = make_float4(gate(gs.x, us.x), gate(gs.y, us.y), gate(gs.z, us.z), gate(gs.w, us.w));
+                const int f = (n0 >> 1) + 8 * t + 4 * h;
+                if (f < out_n) store4<OutT>(Y + (int64_t)m * out_n + f, o, vec, out_n - f);
+            }
+        }
+    }
+    __syncwarp();
+    cluster_sync();                                                           // nobody leaves while its tile is being read
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -398,18 +491,6 @@ gemm_tcgen05_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
     }
 }
 
-// out[m, n] = sum over splits of part[s, m, n], in split order.
-template <typename OutT>
-__global__ void splitk_reduce_kernel(const float* __restrict__ part, OutT* __restrict__ out, int64_t count, int splits) {
-    pdl_launch_dependents();
-    pdl_wait();
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
-        float sum = 0.0f;
-        for (int s = 0; s < splits; ++s) sum += part[s * count + i];
-        out[i] = to_out<OutT>(sum);
-    }
-}
-
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -439,41 +520,73 @@ bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) 
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int STAGES, typename OutT>
-int launch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int splits, int* status, cudaStream_t stream) {
-    using S = Smem<BN, STAGES>;
+int sm_count() {
+    static int count = 0;
+    if (count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+    }
+    return count;
+}
+
+// K ranges (blocks per cluster) for a matrix of N rows: the largest power of two up to the portable
+// cluster size that keeps the grid within 1.75 blocks per SM (two fit) and leaves every block 16 K steps
+// (measured on the projections of an 8B-sized layer).  It depends on N and K only, so the summation
+// order of an output does not depend on the number of rows of X.
+int mid_splits(int N, int K) {
+    const int tiles = (N + BM - 1) / BM, nkb = (K + BK - 1) / BK;
+    int s = 1;
+    while (s < 8 && tiles * (2 * s) * 4 <= sm_count() * 7 && nkb / (2 * s) >= 16) s *= 2;
+    return s;
+}
+
+template <int MT, int STAGES, int MINB, bool GATED, typename OutT>
+int launch_mid(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int splits, int* status, cudaStream_t stream) {
+    constexpr int SMEM = STAGES * (BM * BK * 2 + MT * BK * 2) + 1024 + 256;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, OutT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_mid_kernel<MT, STAGES, MINB, GATED, OutT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     CUtensorMap map_w, map_x;
-    if (!make_map(&map_w, W, N, K, BM) || !make_map(&map_x, X, M, K, BN)) return Q3_ERR_BAD_SIZE;
-    const dim3 grid((N + BM - 1) / BM, (M + BN - 1) / BN, splits);
-    return (int)q3_launch(gemm_tcgen05_kernel<BN, STAGES, OutT>, grid, dim3(THREADS), (size_t)S::TOTAL, stream, map_w, map_x,
-                          Y, M, N, K, status);
+    if (!make_map(&map_w, W, N, K, BM) || !make_map(&map_x, X, M, K, MT)) return Q3_ERR_BAD_SIZE;
+    const dim3 grid((N + BM - 1) / BM, splits);
+    return (int)q3_launch_cluster(gemm_tcgen05_mid_kernel<MT, STAGES, MINB, GATED, OutT>, grid, dim3(THREADS), (size_t)SMEM, stream,
+                                  dim3(1, splits, 1), map_w, map_x, Y, M, N, K, status);
+}
+
+// Stages and blocks per SM come from a sweep on the projections of an 8B-sized layer: a grid that fits
+// the GPU at two blocks per SM wants the deeper ring; a grid of many waves (the output projection onto the
+// vocabulary) wants three blocks per SM with a shorter ring, so that one block's start and end hide behind
+// the others' streams.
+template <bool GATED, typename OutT>
+int dispatch_mid(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int splits, int* status, cudaStream_t stream) {
+    const bool waves = (int64_t)((N + BM - 1) / BM) * splits > 2 * sm_count();
+#define Q3_MID(MT, ST, MB) return launch_mid<MT, ST, MB, GATED, OutT>(X, W, Y, M, N, K, splits, status, stream)
+    if (M <= 16) { if (waves) Q3_MID(16, 4, 3); Q3_MID(16, 5, 2); }
+    if (M <= 32) { if (waves) Q3_MID(32, 3, 3); Q3_MID(32, 5, 2); }
+    if (M <= 64) { if (waves) Q3_MID(64, 3, 3); Q3_MID(64, 4, 2); }
+    Q3_MID(128, 3, 2);
+#undef Q3_MID
 }
 
 template <int BN, int STAGES, bool GATED, typename OutT>
 int launch_prompt(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int* status, cudaStream_t stream) {
     constexpr int SMEM = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
     static bool configured = false;
-    static int sm_count = 0;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_prompt_kernel<BN, STAGES, GATED, OutT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
-        int device = 0;
-        cudaGetDevice(&device);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
         configured = true;
     }
     CUtensorMap map_x, map_w;
     if (!make_map(&map_x, X, M, K, BM) || !make_map(&map_w, W, N, K, BN)) return Q3_ERR_BAD_SIZE;
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    const int blocks = tiles < sm_count ? tiles : sm_count;
+    const int blocks = tiles < sm_count() ? tiles : sm_count();
     return (int)q3_launch(gemm_tcgen05_prompt_kernel<BN, STAGES, GATED, OutT>, dim3(blocks), dim3(THREADS), (size_t)SMEM, stream,
                           map_x, map_w, Y, M, N, K, status);
 }
@@ -507,49 +620,25 @@ Q3_EXPORT int q3_gemm_tcgen05_prompt_gated_bf16(const void* X, const void* W, vo
     return launch_prompt<256, 4, true, bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, status, (cudaStream_t)stream_);
 }
 
-// Direct product (one K range per tile).  `tile_n` picks the token tile: 16, 32, 64, 128 or 256.
-// `status` is a device int that a kernel sets to 1/2/3 if a bounded wait ran out (0 otherwise).
-Q3_EXPORT int q3_gemm_tcgen05_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int tile_n,
-                                   int* status, void* stream_) {
+// The weights-first form for 1..128 rows of X.  `splits` K ranges per tile of 128 rows of W (one cluster;
+// 0 = chosen from N and K).  `gated`: W [N, K] holds gate and up rows interleaved in blocks of eight and
+// Y is [M, N/2] = round(silu(g)) * u.  `status` is a device int that a kernel sets to 1/2/3 if a bounded
+// wait ran out (0 otherwise).
+Q3_EXPORT int q3_gemm_tcgen05_mid_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int gated,
+                                       int splits, int* status, void* stream_) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 != 0) return Q3_ERR_BAD_SIZE;
+    if (K <= 0 || K % 8 != 0 || M > 128 || splits < 0 || splits > 8 || (gated && N % 16 != 0)) return Q3_ERR_BAD_SIZE;
     if (!aligned16(X) || !aligned16(W)) return Q3_ERR_MISALIGNED;
     cudaStream_t stream = (cudaStream_t)stream_;
     const bf16* x = (const bf16*)X;
     const bf16* w = (const bf16*)W;
-#define Q3_TC_CASE(BN, ST)                                                                               \
-    if (tile_n == BN)                                                                                    \
-        return out_is_f32 ? launch<BN, ST, float>(x, w, (float*)Y, M, N, K, 1, status, stream)           \
-                          : launch<BN, ST, bf16>(x, w, (bf16*)Y, M, N, K, 1, status, stream);
-    Q3_TC_CASE(16, 8)
-    Q3_TC_CASE(32, 8)
-    Q3_TC_CASE(64, 8)
-    Q3_TC_CASE(128, 6)
-    Q3_TC_CASE(256, 4)
-#undef Q3_TC_CASE
-    return Q3_ERR_BAD_SIZE;
+    if (splits == 0) splits = mid_splits(N, K);
+    if (splits > (K + BK - 1) / BK) splits = (K + BK - 1) / BK;
+    if (gated)
+        return out_is_f32 ? dispatch_mid<true, float>(x, w, (float*)Y, M, N, K, splits, status, stream)
+                          : dispatch_mid<true, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
+    return out_is_f32 ? dispatch_mid<false, float>(x, w, (float*)Y, M, N, K, splits, status, stream)
+                      : dispatch_mid<false, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
 }
 
-// Split-K product for a handful of rows: partial tiles go to `scratch` (float32 [splits, M, N]) and
-// are summed in split order.
-Q3_EXPORT int q3_gemm_tcgen05_splitk_bf16(const void* X, const void* W, void* Y, float* scratch, int M, int N, int K,
-                                          int out_is_f32, int tile_n, int splits, int* status, void* stream_) {
-    if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 != 0 || splits <= 0) return Q3_ERR_BAD_SIZE;
-    if (!aligned16(X) || !aligned16(W)) return Q3_ERR_MISALIGNED;
-    cudaStream_t stream = (cudaStream_t)stream_;
-    const bf16* x = (const bf16*)X;
-    const bf16* w = (const bf16*)W;
-    int rc = Q3_ERR_BAD_SIZE;
-    if (tile_n == 16) rc = launch<16, 8, float>(x, w, scratch, M, N, K, splits, status, stream);
-    if (tile_n == 32) rc = launch<32, 8, float>(x, w, scratch, M, N, K, splits, status, stream);
-    if (tile_n == 64) rc = launch<64, 8, float>(x, w, scratch, M, N, K, splits, status, stream);
-    if (rc != 0) return rc;
-    const int64_t count = (int64_t)M * N;
-    const int blocks = (int)((count + 255) / 256 < 1184 ? (count + 255) / 256 : 1184);
-    if (out_is_f32)
-        return (int)q3_launch(splitk_reduce_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)scratch,
-                              (float*)Y, count, splits);
-    return (int)q3_launch(splitk_reduce_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const float*)scratch, (bf16*)Y,
-                          count, splits);
-}
+Q3_EXPORT int q3_gemm_tcgen05_mid_splits(int N, int K) { return mid_splits(N, K); }

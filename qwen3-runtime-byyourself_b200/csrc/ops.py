@@ -180,6 +180,20 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tenso
     return out
 
 
+def gemm_bf16_any_width(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T for bfloat16 operands of any width K, on the CUDA cores with 32-bit
+    accumulation: the product for widths that the tensor-core kernels refuse (K no multiple of 8)."""
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N) or out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"gemm_bf16_any_width: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    fn = _fn("gemm_f32.cu", "q3_gemm_tn_bf16",
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p])
+    _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), M, N, K, K, K, N,
+              int(out.dtype == torch.float32), _stream()), "gemm_bf16_any_width")
+    return out
+
+
 # ------------------------------------------------------------------ attention
 def qkv_prepare(qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, cos, sin, token_seq, token_pos, page_table,
                 n_tokens: int, nq: int, nkv: int, d: int, eps: float, write_kv: bool = True):
@@ -332,48 +346,36 @@ def tcgen05_status(device) -> int:
     return value
 
 
-def tcgen05_tile(M: int) -> int:
-    """The token tile for M rows: the smallest of 16..256 that covers M, 256 beyond."""
-    for t in (16, 32, 64, 128):
-        if M <= t:
-            return t
-    return 256 if M > 512 else 128
-
-
-def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_n: Optional[int] = None) -> torch.Tensor:
-    """out[M, N] = x[M, K] . w[N, K]^T on the 5th-generation tensor cores (TMA-fed, accumulator in
-    tensor memory); bfloat16 operands, out bfloat16 or float32; K a multiple of 8."""
+def gemm_tcgen05_mid(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: int = 0) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T for up to 128 rows on the 5th-generation tensor cores, weights
+    first: TMA-fed tiles of 128 rows of w, accumulator in tensor memory, K split over the `splits` blocks
+    of a cluster (0 = chosen from N and K) that add their partial tiles through distributed shared
+    memory.  bfloat16 operands, out bfloat16 or float32; K a multiple of 8."""
     M, K = x.shape
     N = w.shape[0]
-    if w.shape[1] != K or out.shape != (M, N) or K % 8 != 0:
-        raise KernelError(f"gemm_tcgen05: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    if w.shape[1] != K or out.shape != (M, N) or K % 8 != 0 or M > 128:
+        raise KernelError(f"gemm_tcgen05_mid: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
     if out.dtype not in (torch.bfloat16, torch.float32):
-        raise KernelError("gemm_tcgen05: output must be bfloat16 or float32")
-    fn = _fn("gemm_tcgen05.cu", "q3_gemm_tcgen05_bf16",
-             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+        raise KernelError("gemm_tcgen05_mid: output must be bfloat16 or float32")
+    fn = _fn("gemm_tcgen05.cu", "q3_gemm_tcgen05_mid_bf16",
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), M, N, K,
-              int(out.dtype == torch.float32), int(tile_n or tcgen05_tile(M)), _status_word(x.device).data_ptr(),
-              _stream()), "gemm_tcgen05")
+              int(out.dtype == torch.float32), 0, int(splits), _status_word(x.device).data_ptr(), _stream()),
+           "gemm_tcgen05_mid")
     return out
 
 
-def gemm_tcgen05_splitk(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, splits: int,
-                        tile_n: Optional[int] = None) -> torch.Tensor:
-    """The same product for at most 64 rows with K split over `splits` blocks; `scratch` is float32
-    with at least splits * M * N elements."""
+def gemm_tcgen05_mid_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: int = 0) -> torch.Tensor:
+    """out[M, N/2] = round(silu(g)) * u for up to 128 rows; `w` [N, K] holds the gate and up rows interleaved
+    in blocks of eight (`interleave_gate_up`); the gating runs where the cluster's partial tiles are added."""
     M, K = x.shape
     N = w.shape[0]
-    if w.shape[1] != K or out.shape != (M, N) or K % 8 != 0 or M > 64:
-        raise KernelError(f"gemm_tcgen05_splitk: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
-    if scratch.numel() < splits * M * N:
-        raise KernelError("gemm_tcgen05_splitk: scratch too small")
-    fn = _fn("gemm_tcgen05.cu", "q3_gemm_tcgen05_splitk_bf16",
-             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"),
-              _dev(scratch, "scratch", torch.float32), M, N, K, int(out.dtype == torch.float32),
-              int(tile_n or tcgen05_tile(M)), int(splits), _status_word(x.device).data_ptr(), _stream()),
-           "gemm_tcgen05_splitk")
-    _count_extra(1)
+    if w.shape[1] != K or out.shape != (M, N // 2) or K % 8 != 0 or N % 16 != 0 or M > 128 or out.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_tcgen05_mid_gated: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    fn = _fn("gemm_tcgen05.cu", "q3_gemm_tcgen05_mid_bf16",
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), M, N, K, 0, 1, int(splits),
+              _status_word(x.device).data_ptr(), _stream()), "gemm_tcgen05_mid_gated")
     return out
 
 

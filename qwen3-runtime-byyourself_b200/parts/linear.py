@@ -3,9 +3,10 @@
 32-bit operands go to the library's own fmaf kernel (true 32-bit, fixed summation
 order).  bfloat16 operands go to the library's own tensor-core kernels: to its
 weight-streaming kernel for the few rows of a decode step and to its TMA + tcgen05
-kernel for prompts; the sizes in between (17..64 rows) and widths that are no multiple
-of 8 go to the cuBLAS product that torch wraps, as every projection does in the
-reference's engine (src/ops/linear.cpp:165-193: cublasGemmEx, bfloat16 in, 32-bit
+kernels beyond (weights first with K split over a cluster up to 128 rows, tokens first
+and persistent for prompts); widths that are no multiple of 8 go to a CUDA-core kernel
+with 32-bit accumulation.  No product goes to a library, where the reference's engine
+calls cublasGemmEx for every projection (src/ops/linear.cpp:165-193: bfloat16 in, 32-bit
 accumulate).  Another kernel can be registered for a shape (`set_bf16_kernel`).
 """
 from __future__ import annotations
@@ -17,8 +18,8 @@ import torch
 from ..csrc import ops
 
 _bf16_kernel: Optional[Callable] = None
-skinny_rows = 16     # up to this many rows the weight-streaming kernel runs
-prompt_rows = 65     # from this many rows on the TMA + tcgen05 kernel runs; in between, the library
+skinny_rows = 8      # up to this many rows the weight-streaming kernel runs
+prompt_rows = 129    # from this many rows on the persistent tokens-first kernel runs; in between, weights first
 
 
 def set_bf16_kernel(fn: Optional[Callable]) -> None:
@@ -41,10 +42,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         return out
     if x.shape[0] <= skinny_rows and ops.gemm_skinny_fits(x.shape[0], x.shape[1]):
         return ops.gemm_skinny(x, w, out)
-    if x.shape[0] >= prompt_rows and x.shape[1] % 8 == 0:
-        return ops.gemm_tcgen05_prompt(x, w, out)
-    if out.dtype == torch.bfloat16:
-        torch.mm(x, w.t(), out=out)
-    else:
-        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
-    return out
+    if x.shape[1] % 8 == 0:
+        if x.shape[0] >= prompt_rows:
+            return ops.gemm_tcgen05_prompt(x, w, out)
+        return ops.gemm_tcgen05_mid(x, w, out)
+    return ops.gemm_bf16_any_width(x, w, out)

@@ -44,6 +44,8 @@ class SwiGLU(Part):
         elif (self.interleaved and ctx.dtype == torch.bfloat16 and N >= linear_module.prompt_rows
                 and self.hidden_size % 8 == 0):
             ops.gemm_tcgen05_prompt_gated(x, self.w_gate_up, act)  # the gating runs in the product's epilogue
+        elif self.interleaved and ctx.dtype == torch.bfloat16 and self.hidden_size % 8 == 0:
+            ops.gemm_tcgen05_mid_gated(x, self.w_gate_up, act)     # 17..128 rows: gating where the partial tiles meet
         else:
             gate_up = ctx.scratch.get("ff.gate_up", (N, 2 * I), ctx.dtype)
             linear(x, self.w_gate_up, gate_up)

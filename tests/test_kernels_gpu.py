@@ -105,6 +105,20 @@ def test_gemm_f32_is_true_32_bit(M, N, K):
     assert torch.equal(one[0], out[M - 1])
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 45, 67), (37, 130, 100), (200, 333, 100), (5, 64, 9)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+def test_bf16_product_of_any_width(M, N, K, out_dtype):
+    """Widths that are no multiple of 8 (the tensor-core kernels refuse them): bfloat16 operands, 32-bit sums."""
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(M * N + K)
+    xd, wd = dev(rng.normal(0, 1, (M, K)), "bfloat16"), dev(rng.normal(0, 1, (N, K)), "bfloat16")
+    out = torch.full((M, N), float("nan"), dtype=DT[out_dtype], device="cuda")
+    ops.gemm_bf16_any_width(xd, wd, out)
+    exact = back(xd) @ back(wd).T
+    bound = 3e-6 * math.sqrt(K) * 4 if out_dtype == "float32" else 0.02 * math.sqrt(K)
+    assert np.max(np.abs(back(out) - exact)) <= bound
+
+
 def paged_case(rng, lengths, nkv, d, dtype, n_spare=3):
     """Random page tables (shuffled pages) for sequences of the given lengths."""
     pages_per_seq = max(-(-n // 64) for n in lengths)
@@ -409,42 +423,50 @@ def test_prefill_attention_tiled_kernel(nq, nkv, d, window):
 
 
 @pytest.mark.parametrize("M,N,K", [(16, 128, 64), (1, 128, 64), (5, 256, 128), (17, 200, 80), (64, 384, 512),
-                                   (100, 301, 96), (128, 128, 4096), (300, 1000, 1024), (2048, 512, 640)])
+                                   (100, 301, 96), (128, 128, 4096), (33, 1000, 1000), (64, 4096, 4096), (24, 130, 12288)])
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
-def test_tcgen05_product(M, N, K, out_dtype):
-    """The TMA + tcgen05 kernel against a 32-bit product of the same bfloat16 operands, for
-    every token tile, ragged edges in all three dimensions, and K that is no multiple of 64."""
+def test_tcgen05_weights_first_product(M, N, K, out_dtype):
+    """The weights-first TMA + tcgen05 kernel against a 32-bit product of the same bfloat16 operands: every
+    token tile, ragged edges in all three dimensions, K that is no multiple of 64, and K split over clusters
+    of every size that fits (1 = no cluster reduction, 3 = uneven ranges, 8 = the largest)."""
     from qwen3_b200.csrc import ops
     g = torch.Generator(device="cuda").manual_seed(M * 7 + N + K)
     x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
     w = torch.randn(N, K, generator=g, device="cuda").to(torch.bfloat16)
     want = (x.double() @ w.double().T)
-    tiles = sorted({ops.tcgen05_tile(M)} | ({16, 64} if M <= 16 else set()) | ({256} if M > 128 else set()))
-    for tile in tiles:
+    for splits in (0, 1, 2, 3, 8):
         out = torch.full((M, N), float("nan"), dtype=DT[out_dtype], device="cuda")
-        ops.gemm_tcgen05(x, w, out, tile_n=tile)
-        assert ops.tcgen05_status("cuda") == 0, f"a wait inside the kernel gave up (tile {tile})"
+        ops.gemm_tcgen05_mid(x, w, out, splits=splits)
+        assert ops.tcgen05_status("cuda") == 0, f"a wait inside the kernel gave up ({splits} K ranges)"
         err = (out.double() - want).abs().max().item()
         bound = 4e-5 * math.sqrt(K) * 4 if out_dtype == "float32" else 0.02 * math.sqrt(K)
-        assert err <= bound, f"tile {tile}: max abs err {err:.3e} > {bound:.3e}"
+        assert err <= bound, f"{splits} K ranges: max abs err {err:.3e} > {bound:.3e}"
 
 
-@pytest.mark.parametrize("M,N,K,splits", [(8, 4096, 4096, 4), (1, 256, 512, 8), (16, 384, 12288, 6), (33, 200, 1000, 3),
-                                          (64, 128, 64, 4)])
-def test_tcgen05_split_k_product(M, N, K, splits):
+@pytest.mark.parametrize("M,inter,K", [(17, 64, 64), (64, 12288, 512), (33, 160, 96), (128, 1000, 256), (40, 112, 1000)])
+def test_tcgen05_weights_first_gated(M, inter, K):
+    """The same kernel with SiLU and gating where the partial tiles are added equals product + silu_mul,
+    bit for bit at the same number of K ranges, and the plain formula within bfloat16 rounding."""
     from qwen3_b200.csrc import ops
-    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    g = torch.Generator(device="cuda").manual_seed(M + inter + K)
     x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
-    w = torch.randn(N, K, generator=g, device="cuda").to(torch.bfloat16)
-    want = (x.double() @ w.double().T)
-    for out_dtype in ("bfloat16", "float32"):
-        out = torch.full((M, N), float("nan"), dtype=DT[out_dtype], device="cuda")
-        scratch = torch.full((splits * M * N,), float("nan"), dtype=torch.float32, device="cuda")
-        ops.gemm_tcgen05_splitk(x, w, out, scratch, splits)
+    gate = (torch.randn(inter, K, generator=g, device="cuda") * 0.2).to(torch.bfloat16)
+    up = (torch.randn(inter, K, generator=g, device="cuda") * 0.2).to(torch.bfloat16)
+    w = ops.interleave_gate_up(gate, up)
+    gd = plain.round_bf16(back(x) @ back(gate).T)
+    ud = plain.round_bf16(back(x) @ back(up).T)
+    want = plain.silu_multiply(gd, ud, plain.round_bf16)
+    scale = max(1.0, float(np.abs(want).max()))
+    for splits in (0, 1, 4):
+        fused = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.gemm_tcgen05_mid_gated(x, w, fused, splits=splits)
+        gate_up = torch.empty(M, 2 * inter, dtype=torch.bfloat16, device="cuda")
+        ops.gemm_tcgen05_mid(x, w, gate_up, splits=splits)
+        two = torch.empty_like(fused)
+        ops.silu_mul(gate_up, two, interleaved=True)
         assert ops.tcgen05_status("cuda") == 0
-        err = (out.double() - want).abs().max().item()
-        bound = 4e-5 * math.sqrt(K) * 4 if out_dtype == "float32" else 0.02 * math.sqrt(K)
-        assert err <= bound, f"max abs err {err:.3e} > {bound:.3e}"
+        assert torch.equal(fused, two)
+        assert np.max(np.abs(back(fused) - want)) <= 2e-2 * scale
 
 
 @pytest.mark.parametrize("M,inter,K", [(1, 64, 64), (8, 12288, 4096), (3, 160, 96), (16, 1000, 256), (9, 112, 80)])
