@@ -141,7 +141,8 @@ template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float4 v, bool
     for (int i = 0; i < 4 && i < valid; ++i) p[i] = __float2bfloat16_rn(e[i]);
 }
 
-// Grid (tiles of 128 rows of W, K ranges); the blocks of one tile form a cluster (1, gridDim.y, 1).
+// Grid (tiles of 128 rows of W, K ranges, tiles of MT tokens); the blocks of one tile form a cluster
+// (1, gridDim.y, 1).
 // GATED: W holds gate and up rows interleaved in blocks of eight and Y is [M, N/2] = round(silu(g)) * u.
 template <int MT, int STAGES, int MINB, bool GATED, typename OutT>
 __global__ void __launch_bounds__(THREADS, MINB)
@@ -156,7 +157,7 @@ gemm_tcgen05_mid_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     const uint32_t bars = base + STAGES * STAGE_BYTES;                    // full[STAGES], empty[STAGES], done, tmem slot
     const uint32_t bar_done = bars + 2 * STAGES * 8, tmem_slot = bar_done + 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BM;
+    const int n0 = blockIdx.x * BM, m0 = blockIdx.z * MT;
     const uint32_t rank = cluster_rank(), ranks = gridDim.y;
     const int nkb_all = (K + BK - 1) / BK;
     const int kb_begin = (int)(((int64_t)rank * nkb_all) / ranks);
@@ -203,7 +204,7 @@ gemm_tcgen05_mid_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                 mbar_expect_tx(bars + s * 8, STAGE_BYTES);
                 tma_load_2d(a, &map_w, bars + s * 8, (kb_begin + i) * BK, n0);      // weights: independent of the
                 if (i == 0) pdl_wait();                                              // kernel before; X is not
-                tma_load_2d(b, &map_x, bars + s * 8, (kb_begin + i) * BK, 0);
+                tma_load_2d(b, &map_x, bars + s * 8, (kb_begin + i) * BK, m0);
             }
         }
     } else if (warp == 1) {
@@ -260,10 +261,11 @@ gemm_tcgen05_mid_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         constexpr int GROUPS = GATED ? 16 : 32;                               // groups of four outputs per token and tile
         const int my_tokens = (MT - (int)rank + (int)ranks - 1) / (int)ranks;
         for (int idx = threadIdx.x; idx < my_tokens * GROUPS; idx += THREADS) {
-            const int m = (idx / GROUPS) * (int)ranks + (int)rank, g = idx % GROUPS;
+            const int local = (idx / GROUPS) * (int)ranks + (int)rank, g = idx % GROUPS;
+            const int m = m0 + local;
             if (m >= M) continue;
             if constexpr (!GATED) {
-                const uint32_t addr = base + (uint32_t)(m * PART_LD + 4 * g) * 4u;
+                const uint32_t addr = base + (uint32_t)(local * PART_LD + 4 * g) * 4u;
                 float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
                 for (uint32_t s = 0; s < ranks; ++s) {
                     const float4 v = ld_cluster_f4(map_to_rank(addr, s));
@@ -274,7 +276,7 @@ gemm_tcgen05_mid_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
             } else {
                 // rows 16t + 4h .. +3 are gates, rows 16t + 8 + 4h .. +3 the ups of features 8t + 4h .. +3
                 const int t = g >> 1, h = g & 1;
-                const uint32_t addr_g = base + (uint32_t)(m * PART_LD + 16 * t + 4 * h) * 4u, addr_u = addr_g + 32u;
+                const uint32_t addr_g = base + (uint32_t)(local * PART_LD + 16 * t + 4 * h) * 4u, addr_u = addr_g + 32u;
                 float4 gs = make_float4(0.f, 0.f, 0.f, 0.f), us = gs;
                 for (uint32_t s = 0; s < ranks; ++s) {
                     const float4 a = ld_cluster_f4(map_to_rank(addr_g, s)), b = ld_cluster_f4(map_to_rank(addr_u, s));
@@ -531,13 +533,14 @@ int sm_count() {
 }
 
 // K ranges (blocks per cluster) for a matrix of N rows: the largest power of two up to the portable
-// cluster size that keeps the grid within 1.75 blocks per SM (two fit) and leaves every block 16 K steps
-// (measured on the projections of an 8B-sized layer).  It depends on N and K only, so the summation
-// order of an output does not depend on the number of rows of X.
-int mid_splits(int N, int K) {
-    const int tiles = (N + BM - 1) / BM, nkb = (K + BK - 1) / BK;
+// cluster size that keeps the grid within 1.75 blocks per SM (two fit; within one block per SM for the
+// 256-token tile, of which one fits) and leaves every block 16 K steps (measured on the projections of
+// an 8B-sized layer).  `token_tiles` = 0 stands for at most 128 tokens.
+int mid_splits(int N, int K, int token_tiles) {
+    const int tiles = ((N + BM - 1) / BM) * (token_tiles > 0 ? token_tiles : 1), nkb = (K + BK - 1) / BK;
+    const int limit = token_tiles > 0 ? sm_count() : sm_count() * 7 / 4;
     int s = 1;
-    while (s < 8 && tiles * (2 * s) * 4 <= sm_count() * 7 && nkb / (2 * s) >= 16) s *= 2;
+    while (s < 8 && tiles * (2 * s) <= limit && nkb / (2 * s) >= 16) s *= 2;
     return s;
 }
 
@@ -553,7 +556,7 @@ int launch_mid(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int s
     }
     CUtensorMap map_w, map_x;
     if (!make_map(&map_w, W, N, K, BM) || !make_map(&map_x, X, M, K, MT)) return Q3_ERR_BAD_SIZE;
-    const dim3 grid((N + BM - 1) / BM, splits);
+    const dim3 grid((N + BM - 1) / BM, splits, (M + MT - 1) / MT);
     return (int)q3_launch_cluster(gemm_tcgen05_mid_kernel<MT, STAGES, MINB, GATED, OutT>, grid, dim3(THREADS), (size_t)SMEM, stream,
                                   dim3(1, splits, 1), map_w, map_x, Y, M, N, K, status);
 }
@@ -569,7 +572,8 @@ int dispatch_mid(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int
     if (M <= 16) { if (waves) Q3_MID(16, 4, 3); Q3_MID(16, 5, 2); }
     if (M <= 32) { if (waves) Q3_MID(32, 3, 3); Q3_MID(32, 5, 2); }
     if (M <= 64) { if (waves) Q3_MID(64, 3, 3); Q3_MID(64, 4, 2); }
-    Q3_MID(128, 3, 2);
+    if (M <= 128) Q3_MID(128, 3, 2);
+    Q3_MID(256, 4, 1);                  // one or more tiles of 256 tokens (grid.z)
 #undef Q3_MID
 }
 
@@ -620,19 +624,19 @@ Q3_EXPORT int q3_gemm_tcgen05_prompt_gated_bf16(const void* X, const void* W, vo
     return launch_prompt<256, 4, true, bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, status, (cudaStream_t)stream_);
 }
 
-// The weights-first form for 1..128 rows of X.  `splits` K ranges per tile of 128 rows of W (one cluster;
+// The weights-first form for a few hundred rows of X at most (W is read once per 256 rows).  `splits` K ranges per tile of 128 rows of W (one cluster;
 // 0 = chosen from N and K).  `gated`: W [N, K] holds gate and up rows interleaved in blocks of eight and
 // Y is [M, N/2] = round(silu(g)) * u.  `status` is a device int that a kernel sets to 1/2/3 if a bounded
 // wait ran out (0 otherwise).
 Q3_EXPORT int q3_gemm_tcgen05_mid_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int gated,
                                        int splits, int* status, void* stream_) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 != 0 || M > 128 || splits < 0 || splits > 8 || (gated && N % 16 != 0)) return Q3_ERR_BAD_SIZE;
+    if (K <= 0 || K % 8 != 0 || M > 256 * 1024 || splits < 0 || splits > 8 || (gated && N % 16 != 0)) return Q3_ERR_BAD_SIZE;
     if (!aligned16(X) || !aligned16(W)) return Q3_ERR_MISALIGNED;
     cudaStream_t stream = (cudaStream_t)stream_;
     const bf16* x = (const bf16*)X;
     const bf16* w = (const bf16*)W;
-    if (splits == 0) splits = mid_splits(N, K);
+    if (splits == 0) splits = mid_splits(N, K, M <= 128 ? 0 : (M + 255) / 256);
     if (splits > (K + BK - 1) / BK) splits = (K + BK - 1) / BK;
     if (gated)
         return out_is_f32 ? dispatch_mid<true, float>(x, w, (float*)Y, M, N, K, splits, status, stream)
@@ -641,4 +645,4 @@ Q3_EXPORT int q3_gemm_tcgen05_mid_bf16(const void* X, const void* W, void* Y, in
                       : dispatch_mid<false, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
 }
 
-Q3_EXPORT int q3_gemm_tcgen05_mid_splits(int N, int K) { return mid_splits(N, K); }
+Q3_EXPORT int q3_gemm_tcgen05_mid_splits(int N, int K, int M) { return mid_splits(N, K, M <= 128 ? 0 : (M + 255) / 256); }

@@ -347,13 +347,13 @@ def tcgen05_status(device) -> int:
 
 
 def gemm_tcgen05_mid(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: int = 0) -> torch.Tensor:
-    """out[M, N] = x[M, K] . w[N, K]^T for up to 128 rows on the 5th-generation tensor cores, weights
-    first: TMA-fed tiles of 128 rows of w, accumulator in tensor memory, K split over the `splits` blocks
+    """out[M, N] = x[M, K] . w[N, K]^T for a few hundred rows at most on the 5th-generation tensor cores,
+    weights first: TMA-fed tiles of 128 rows of w, accumulator in tensor memory, K split over the `splits` blocks
     of a cluster (0 = chosen from N and K) that add their partial tiles through distributed shared
     memory.  bfloat16 operands, out bfloat16 or float32; K a multiple of 8."""
     M, K = x.shape
     N = w.shape[0]
-    if w.shape[1] != K or out.shape != (M, N) or K % 8 != 0 or M > 128:
+    if w.shape[1] != K or out.shape != (M, N) or K % 8 != 0:
         raise KernelError(f"gemm_tcgen05_mid: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError("gemm_tcgen05_mid: output must be bfloat16 or float32")
@@ -365,12 +365,21 @@ def gemm_tcgen05_mid(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits
     return out
 
 
+def gemm_tcgen05_mid_splits(M: int, N: int, K: int) -> int:
+    """The number of K ranges `gemm_tcgen05_mid` chooses for this shape."""
+    from .build import load_library
+    lib = load_library("gemm_tcgen05.cu", ())
+    lib.q3_gemm_tcgen05_mid_splits.argtypes = [c_int, c_int, c_int]
+    lib.q3_gemm_tcgen05_mid_splits.restype = c_int
+    return int(lib.q3_gemm_tcgen05_mid_splits(N, K, M))
+
+
 def gemm_tcgen05_mid_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: int = 0) -> torch.Tensor:
-    """out[M, N/2] = round(silu(g)) * u for up to 128 rows; `w` [N, K] holds the gate and up rows interleaved
+    """out[M, N/2] = round(silu(g)) * u for a few hundred rows at most; `w` [N, K] holds the gate and up rows interleaved
     in blocks of eight (`interleave_gate_up`); the gating runs where the cluster's partial tiles are added."""
     M, K = x.shape
     N = w.shape[0]
-    if w.shape[1] != K or out.shape != (M, N // 2) or K % 8 != 0 or N % 16 != 0 or M > 128 or out.dtype != torch.bfloat16:
+    if w.shape[1] != K or out.shape != (M, N // 2) or K % 8 != 0 or N % 16 != 0 or out.dtype != torch.bfloat16:
         raise KernelError(f"gemm_tcgen05_mid_gated: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
     fn = _fn("gemm_tcgen05.cu", "q3_gemm_tcgen05_mid_bf16",
              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])

@@ -11,6 +11,7 @@ accumulate).  Another kernel can be registered for a shape (`set_bf16_kernel`).
 """
 from __future__ import annotations
 
+import functools
 from typing import Callable, Optional
 
 import torch
@@ -19,13 +20,42 @@ from ..csrc import ops
 
 _bf16_kernel: Optional[Callable] = None
 skinny_rows = 8      # up to this many rows the weight-streaming kernel runs
-prompt_rows = 129    # from this many rows on the persistent tokens-first kernel runs; in between, weights first
 
 
 def set_bf16_kernel(fn: Optional[Callable]) -> None:
-    """`fn(x, w, out) -> bool` may take a bfloat16 product; False hands it to the library."""
+    """`fn(x, w, out) -> bool` may take a bfloat16 product; False hands it to the kernels below."""
     global _bf16_kernel
     _bf16_kernel = fn
+
+
+# Microseconds per 64-wide K step of a tile, and per block for start and end, measured on B200 (the
+# 128-token tiles are bound by what one SM can pull from the L2, so a step costs its bytes).
+_STEP_US = {"prompt256": 0.40, "prompt128": 0.29, "weights_first": 0.40}
+
+
+@functools.lru_cache(maxsize=4096)
+def tcgen05_form(M: int, N: int, K: int, gated: bool = False) -> str:
+    """Which form of the tcgen05 product takes M rows (M > skinny_rows, K a multiple of 8): weights first
+    (K split over a cluster; the only form that fills the GPU when M and N give few tiles), or tokens first
+    and persistent with 128 x 128 or 128 x 256 tiles.  A small cost model: waves of blocks times K steps."""
+    if M <= 128:
+        return "weights_first"
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    nkb = -(-K // 64)
+
+    def waves(blocks):
+        return -(-blocks // sms)
+
+    cost = {}
+    for form, bn in (("prompt256", 256), ("prompt128", 128)):
+        if gated and bn == 128:
+            continue                                     # the gated epilogue exists for the 256-row tile
+        cost[form] = waves(-(-M // 128) * -(-N // bn)) * nkb * _STEP_US[form] + 3.0
+    if M <= 1024:
+        splits = ops.gemm_tcgen05_mid_splits(M, N, K)
+        blocks = -(-N // 128) * -(-M // 256) * splits
+        cost["weights_first"] = waves(blocks) * (-(-nkb // splits) * _STEP_US["weights_first"] + (10.0 if splits > 1 else 5.0))
+    return min(cost, key=cost.get)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -40,10 +70,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         raise ops.KernelError("linear: CUDA tensors only")
     if _bf16_kernel is not None and _bf16_kernel(x, w, out):
         return out
-    if x.shape[0] <= skinny_rows and ops.gemm_skinny_fits(x.shape[0], x.shape[1]):
+    M, K = x.shape
+    if K % 8 != 0:
+        return ops.gemm_bf16_any_width(x, w, out)
+    if M <= skinny_rows:
         return ops.gemm_skinny(x, w, out)
-    if x.shape[1] % 8 == 0:
-        if x.shape[0] >= prompt_rows:
-            return ops.gemm_tcgen05_prompt(x, w, out)
+    form = tcgen05_form(M, w.shape[0], K)
+    if form == "weights_first":
         return ops.gemm_tcgen05_mid(x, w, out)
-    return ops.gemm_bf16_any_width(x, w, out)
+    return ops.gemm_tcgen05_prompt(x, w, out, tile_n=256 if form == "prompt256" else 128)

@@ -38,14 +38,13 @@ class SwiGLU(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         N, I = ctx.n_tokens, self.intermediate_size
         act = ctx.scratch.get("ff.act", (N, I), ctx.dtype)
-        if (self.interleaved and ctx.dtype == torch.bfloat16 and N <= linear_module.skinny_rows
-                and ops.gemm_skinny_fits(N, self.hidden_size)):
+        fused = self.interleaved and ctx.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
+        if fused and N <= linear_module.skinny_rows:
             ops.gemm_skinny_gated(x, self.w_gate_up, act)          # product, SiLU and gating in one kernel
-        elif (self.interleaved and ctx.dtype == torch.bfloat16 and N >= linear_module.prompt_rows
-                and self.hidden_size % 8 == 0):
+        elif fused and linear_module.tcgen05_form(N, 2 * I, self.hidden_size, gated=True) == "weights_first":
+            ops.gemm_tcgen05_mid_gated(x, self.w_gate_up, act)     # gating where the cluster's partial tiles meet
+        elif fused:
             ops.gemm_tcgen05_prompt_gated(x, self.w_gate_up, act)  # the gating runs in the product's epilogue
-        elif self.interleaved and ctx.dtype == torch.bfloat16 and self.hidden_size % 8 == 0:
-            ops.gemm_tcgen05_mid_gated(x, self.w_gate_up, act)     # 17..128 rows: gating where the partial tiles meet
         else:
             gate_up = ctx.scratch.get("ff.gate_up", (N, 2 * I), ctx.dtype)
             linear(x, self.w_gate_up, gate_up)

@@ -423,7 +423,8 @@ def test_prefill_attention_tiled_kernel(nq, nkv, d, window):
 
 
 @pytest.mark.parametrize("M,N,K", [(16, 128, 64), (1, 128, 64), (5, 256, 128), (17, 200, 80), (64, 384, 512),
-                                   (100, 301, 96), (128, 128, 4096), (33, 1000, 1000), (64, 4096, 4096), (24, 130, 12288)])
+                                   (100, 301, 96), (128, 128, 4096), (33, 1000, 1000), (64, 4096, 4096), (24, 130, 12288),
+                                   (129, 200, 136), (256, 512, 2048), (300, 1000, 1024), (700, 130, 520)])
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
 def test_tcgen05_weights_first_product(M, N, K, out_dtype):
     """The weights-first TMA + tcgen05 kernel against a 32-bit product of the same bfloat16 operands: every
@@ -443,7 +444,8 @@ def test_tcgen05_weights_first_product(M, N, K, out_dtype):
         assert err <= bound, f"{splits} K ranges: max abs err {err:.3e} > {bound:.3e}"
 
 
-@pytest.mark.parametrize("M,inter,K", [(17, 64, 64), (64, 12288, 512), (33, 160, 96), (128, 1000, 256), (40, 112, 1000)])
+@pytest.mark.parametrize("M,inter,K", [(17, 64, 64), (64, 12288, 512), (33, 160, 96), (128, 1000, 256), (40, 112, 1000),
+                                       (200, 160, 1024), (513, 72, 96)])
 def test_tcgen05_weights_first_gated(M, inter, K):
     """The same kernel with SiLU and gating where the partial tiles are added equals product + silu_mul,
     bit for bit at the same number of K ranges, and the plain formula within bfloat16 rounding."""
