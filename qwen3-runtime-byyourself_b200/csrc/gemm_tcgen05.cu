@@ -493,6 +493,201 @@ gemm_tcgen05_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The prompt form on pairs of SMs (tcgen05 cta_group::2).  A tile of 128 tokens by 256 rows of W
+// costs an SM 48 KB of shared-memory fill per K step of 64, and what an SM can pull from the L2 then
+// bounds the product below what its tensor cores could do.  Here two blocks on neighbouring SMs (a
+// cluster of two) share one tile of 256 tokens by 256 rows of W: each loads its own 128 tokens and
+// only HALF of the W tile (its 128 rows), the instruction reads both halves from both blocks'
+// shared memory, and each block's tensor memory receives the accumulator of its own 128 tokens.
+// Per K step a block now fills 32 KB for the same arithmetic.
+//
+// Protocol (rank 0 of the pair leads):
+//   full[s]       in the leader: both blocks' TMA loads report their bytes there
+//   empty[s]      in each block: the leader's tcgen05.commit arrives at both (multicast)
+//   acc_full[b]   in each block: likewise, when a tile's accumulator is complete
+//   acc_empty[b]  in the leader: the eight drain warps of both blocks arrive there
+// Only the leader issues tcgen05.mma.  Every wait is bounded as above, and both blocks meet at a
+// cluster barrier before either leaves (the peer's shared memory and barriers are in use until then).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_in_leader, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar_in_leader), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives, once the MMAs issued so far are done, at the barrier at this offset in both blocks of the pair.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+template <int STAGES, bool GATED, typename OutT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                         OutT* __restrict__ Y, int M, int N, int K, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    constexpr int BN = 256, PAIR_M = 2 * BM;
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = 2 * BN;                    // two accumulators of 128 tokens x 256 rows of W
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = base + STAGES * STAGE_BYTES;       // full[S], empty[S], acc_full[2], acc_empty[2], slot
+    const uint32_t bar_acc_full = bars + 2 * STAGES * 8, bar_acc_empty = bar_acc_full + 16, tmem_slot = bar_acc_empty + 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const int pairs_m = (M + PAIR_M - 1) / PAIR_M, n_tiles = (N + BN - 1) / BN, tiles = pairs_m * n_tiles;
+    const int first = blockIdx.x >> 1, stride = gridDim.x >> 1;
+    const int nkb = (K + BK - 1) / BK;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bars + s * 8, 1);
+            mbar_init(bars + (STAGES + s) * 8, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_acc_full + b * 8, 1);
+            mbar_init(bar_acc_empty + b * 8, 8);             // one arrival per drain warp of the pair
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                           // the peer's barriers exist before anything signals them
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_wait();                                       // X is the output of the kernel before
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = first; tile < tiles && ok; tile += stride) {
+                const int m0 = (tile % pairs_m) * PAIR_M + (int)rank * BM;
+                const int n0 = (tile / pairs_m) * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(bars + (STAGES + s) * 8, ((it / STAGES) & 1u) ^ 1u);
+                    if (!ok) { atomicExch(status, 1); break; }
+                    const uint32_t a = base + s * STAGE_BYTES, b = a + A_BYTES;
+                    const uint32_t full_in_leader = map_to_rank(bars + s * 8, 0);
+                    if (rank == 0) mbar_expect_tx(bars + s * 8, 2 * STAGE_BYTES);       // both blocks' bytes
+                    tma_load_2d_pair(a, &map_x, full_in_leader, kb * BK, m0);
+                    tma_load_2d_pair(b, &map_w, full_in_leader, kb * BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_mn(PAIR_M, BN);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int tile = first; tile < tiles && ok; tile += stride, ++local) {
+                const uint32_t buf = local & 1u;
+                ok = mbar_wait(bar_acc_empty + buf * 8, ((local >> 1) & 1u) ^ 1u);      // both blocks have drained it
+                if (!ok) { atomicExch(status, 4); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(bars + s * 8, (it / STAGES) & 1u);
+                    if (!ok) { atomicExch(status, 2); break; }
+                    tc_fence_after();
+                    const uint32_t a = base + s * STAGE_BYTES, b = a + A_BYTES;
+                    const uint64_t da = make_desc(a), db = make_desc(b);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc_mma_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit_pair(bars + (STAGES + s) * 8);
+                }
+                tc_commit_pair(bar_acc_full + buf * 8);
+            }
+        }
+    } else {
+        pdl_wait();
+        const int lane_base = (warp & 3) * 32;
+        const bool vec_ok = ((GATED ? (N >> 1) : N) % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15u) == 0);
+        uint32_t local = 0;
+        for (int tile = first; tile < tiles; tile += stride, ++local) {
+            const uint32_t buf = local & 1u;
+            const int m0 = (tile % pairs_m) * PAIR_M + (int)rank * BM, n0 = (tile / pairs_m) * BN;
+            if (!mbar_wait(bar_acc_full + buf * 8, (local >> 1) & 1u)) {
+                if (lane == 0) atomicExch(status, 3);
+                break;
+            }
+            tc_fence_after();
+            const int m = m0 + lane_base + lane;
+            OutT* row = Y + (int64_t)m * (GATED ? (N >> 1) : N) + (GATED ? (n0 >> 1) : n0);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tc_ld32(tmem_base + ((uint32_t)lane_base << 16) + buf * BN + (uint32_t)c, r);
+                tc_wait_ld();
+                if constexpr (GATED) {
+                    // columns c..c+31 = gate[8] up[8] gate[8] up[8] of 16 features (src/ops/elementwise.cu:47-65)
+                    if (m < M) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int n = n0 + c + h * 16;           // first gate column of this block
+                            uint32_t packed[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const float g = round_to<bf16>(__uint_as_float(r[h * 16 + e]));
+                                const float u = round_to<bf16>(__uint_as_float(r[h * 16 + 8 + e]));
+                                packed[e] = __float_as_uint(round_to<bf16>(g / (1.0f + expf(-g))) * u);
+                            }
+                            OutT* dst = row + ((c + h * 16) >> 1);
+                            if (n + 16 <= N && vec_ok) {
+                                store_run8<OutT>(dst, packed);
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e)
+                                    if (n + 8 + e < N) dst[e] = to_out<OutT>(__uint_as_float(packed[e]));
+                            }
+                        }
+                    }
+                } else if (m < M) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        const int n = n0 + c + j;
+                        if (vec_ok && n + 8 <= N) {
+                            store_run8<OutT>(row + c + j, r + j);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                if (n + e < N) row[c + j + e] = to_out<OutT>(__uint_as_float(r[j + e]));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_rank(bar_acc_empty + buf * 8, 0));   // this warp's share is drained
+        }
+    }
+    tc_fence_before();
+    __syncwarp();
+    cluster_sync();                                           // the peer reads this block's memory and barriers until here
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -595,6 +790,24 @@ int launch_prompt(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, in
                           map_x, map_w, Y, M, N, K, status);
 }
 
+template <int STAGES, bool GATED, typename OutT>
+int launch_pair(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int* status, cudaStream_t stream) {
+    constexpr int SMEM = STAGES * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<STAGES, GATED, OutT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    CUtensorMap map_x, map_w;
+    if (!make_map(&map_x, X, M, K, BM) || !make_map(&map_w, W, N, K, 128)) return Q3_ERR_BAD_SIZE;
+    const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+    const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+    return (int)q3_launch_cluster(gemm_tcgen05_pair_kernel<STAGES, GATED, OutT>, dim3(2 * pairs), dim3(THREADS), (size_t)SMEM,
+                                  stream, dim3(2, 1, 1), map_x, map_w, Y, M, N, K, status);
+}
+
 }  // namespace
 
 // The prompt form: persistent blocks, 128 tokens x `tile_n` (128 or 256) rows of W per tile.
@@ -613,6 +826,21 @@ Q3_EXPORT int q3_gemm_tcgen05_prompt_bf16(const void* X, const void* W, void* Y,
         return out_is_f32 ? launch_prompt<128, 6, false, float>(x, w, (float*)Y, M, N, K, status, stream)
                           : launch_prompt<128, 6, false, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
     return Q3_ERR_BAD_SIZE;
+}
+
+// The prompt form on pairs of SMs: tiles of 256 tokens x 256 rows of W, each block of a pair loading half of
+// the W tile.  `gated` as below (bfloat16 output only).
+Q3_EXPORT int q3_gemm_tcgen05_pair_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int gated,
+                                        int* status, void* stream_) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || (gated && (N % 16 != 0 || out_is_f32))) return Q3_ERR_BAD_SIZE;
+    if (!aligned16(X) || !aligned16(W)) return Q3_ERR_MISALIGNED;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const bf16* x = (const bf16*)X;
+    const bf16* w = (const bf16*)W;
+    if (gated) return launch_pair<6, true, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
+    return out_is_f32 ? launch_pair<6, false, float>(x, w, (float*)Y, M, N, K, status, stream)
+                      : launch_pair<6, false, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
 }
 
 // W [N, K] holds gate and up rows interleaved in blocks of eight; Y [M, N/2] = round(silu(g)) * u, bfloat16.

@@ -3,8 +3,8 @@
 32-bit operands go to the library's own fmaf kernel (true 32-bit, fixed summation
 order).  bfloat16 operands go to the library's own tensor-core kernels: to its
 weight-streaming kernel for the few rows of a decode step and to its TMA + tcgen05
-kernels beyond (weights first with K split over a cluster up to 128 rows, tokens first
-and persistent for prompts); widths that are no multiple of 8 go to a CUDA-core kernel
+kernels beyond (weights first with K split over a cluster for up to a few hundred rows,
+tokens first and persistent on pairs of SMs for prompts); widths that are no multiple of 8 go to a CUDA-core kernel
 with 32-bit accumulation.  No product goes to a library, where the reference's engine
 calls cublasGemmEx for every projection (src/ops/linear.cpp:165-193: bfloat16 in, 32-bit
 accumulate).  Another kernel can be registered for a shape (`set_bf16_kernel`).
@@ -28,33 +28,32 @@ def set_bf16_kernel(fn: Optional[Callable]) -> None:
     _bf16_kernel = fn
 
 
-# Microseconds per 64-wide K step of a tile, and per block for start and end, measured on B200 (the
-# 128-token tiles are bound by what one SM can pull from the L2, so a step costs its bytes).
-_STEP_US = {"prompt256": 0.40, "prompt128": 0.29, "weights_first": 0.40}
+# Microseconds per 64-wide K step of a tile and per block for its start and end, measured on B200.
+_STEP_US = {"pair": 0.33, "prompt128": 0.29, "weights_first": 0.40}
+_BLOCK_US = {"pair": 8.0, "prompt128": 5.0}
 
 
 @functools.lru_cache(maxsize=4096)
 def tcgen05_form(M: int, N: int, K: int, gated: bool = False) -> str:
     """Which form of the tcgen05 product takes M rows (M > skinny_rows, K a multiple of 8): weights first
     (K split over a cluster; the only form that fills the GPU when M and N give few tiles), or tokens first
-    and persistent with 128 x 128 or 128 x 256 tiles.  A small cost model: waves of blocks times K steps."""
+    and persistent, on single SMs with 128 x 128 tiles or on pairs of SMs with 256 x 256 tiles.  A small
+    cost model: waves of blocks times K steps."""
     if M <= 128:
         return "weights_first"
     sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
     nkb = -(-K // 64)
 
-    def waves(blocks):
-        return -(-blocks // sms)
+    def waves(blocks, slots):
+        return -(-blocks // slots)
 
-    cost = {}
-    for form, bn in (("prompt256", 256), ("prompt128", 128)):
-        if gated and bn == 128:
-            continue                                     # the gated epilogue exists for the 256-row tile
-        cost[form] = waves(-(-M // 128) * -(-N // bn)) * nkb * _STEP_US[form] + 3.0
+    cost = {"pair": waves(-(-M // 256) * -(-N // 256), sms // 2) * nkb * _STEP_US["pair"] + _BLOCK_US["pair"]}
+    if not gated:                                        # the gated epilogue exists for the 256-row tiles
+        cost["prompt128"] = waves(-(-M // 128) * -(-N // 128), sms) * nkb * _STEP_US["prompt128"] + _BLOCK_US["prompt128"]
     if M <= 1024:
         splits = ops.gemm_tcgen05_mid_splits(M, N, K)
         blocks = -(-N // 128) * -(-M // 256) * splits
-        cost["weights_first"] = waves(blocks) * (-(-nkb // splits) * _STEP_US["weights_first"] + (10.0 if splits > 1 else 5.0))
+        cost["weights_first"] = waves(blocks, sms) * (-(-nkb // splits) * _STEP_US["weights_first"] + (10.0 if splits > 1 else 5.0))
     return min(cost, key=cost.get)
 
 
@@ -78,4 +77,6 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     form = tcgen05_form(M, w.shape[0], K)
     if form == "weights_first":
         return ops.gemm_tcgen05_mid(x, w, out)
-    return ops.gemm_tcgen05_prompt(x, w, out, tile_n=256 if form == "prompt256" else 128)
+    if form == "pair":
+        return ops.gemm_tcgen05_pair(x, w, out)
+    return ops.gemm_tcgen05_prompt(x, w, out, tile_n=128)

@@ -522,6 +522,48 @@ def test_tcgen05_prompt_product(M, N, K, out_dtype):
         assert err <= bound, f"tile {tile}: max abs err {err:.3e} > {bound:.3e}"
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (1, 8, 64), (200, 301, 80), (2048, 1024, 512), (1000, 6144, 4096),
+                                   (4100, 520, 136), (129, 257, 8), (300, 40000, 128)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+def test_tcgen05_pair_product(M, N, K, out_dtype):
+    """The product on pairs of SMs (cta_group::2): one tile and many per pair, ragged edges (a second block
+    whose tokens are all beyond M included), widths that rule out vector stores."""
+    from qwen3_b200.csrc import ops
+    g = torch.Generator(device="cuda").manual_seed(M + 3 * N + K)
+    x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g, device="cuda").to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    out = torch.full((M, N), float("nan"), dtype=DT[out_dtype], device="cuda")
+    ops.gemm_tcgen05_pair(x, w, out)
+    assert ops.tcgen05_status("cuda") == 0, "a wait inside the kernel gave up"
+    err = (out.double() - want).abs().max().item()
+    bound = 4e-5 * math.sqrt(K) * 4 if out_dtype == "float32" else 0.02 * math.sqrt(K)
+    assert err <= bound, f"max abs err {err:.3e} > {bound:.3e}"
+
+
+@pytest.mark.parametrize("M,inter,K", [(128, 128, 64), (300, 160, 96), (2048, 1536, 512), (77, 112, 80)])
+def test_tcgen05_pair_gated_epilogue(M, inter, K):
+    """The pair kernel with SiLU and gating in its epilogue equals its own product + silu_mul, bit for bit."""
+    from qwen3_b200.csrc import ops
+    g = torch.Generator(device="cuda").manual_seed(M + inter + K)
+    x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    gate = (torch.randn(inter, K, generator=g, device="cuda") * 0.2).to(torch.bfloat16)
+    up = (torch.randn(inter, K, generator=g, device="cuda") * 0.2).to(torch.bfloat16)
+    w = ops.interleave_gate_up(gate, up)
+    fused = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tcgen05_pair(x, w, fused, gated=True)
+    gate_up = torch.empty(M, 2 * inter, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tcgen05_pair(x, w, gate_up)
+    two = torch.empty_like(fused)
+    ops.silu_mul(gate_up, two, interleaved=True)
+    assert ops.tcgen05_status("cuda") == 0
+    assert torch.equal(fused, two)
+    gd = plain.round_bf16(back(x) @ back(gate).T)
+    ud = plain.round_bf16(back(x) @ back(up).T)
+    want = plain.silu_multiply(gd, ud, plain.round_bf16)
+    assert np.max(np.abs(back(fused) - want)) <= 2e-2 * max(1.0, float(np.abs(want).max()))
+
+
 @pytest.mark.parametrize("M,inter,K", [(128, 128, 64), (300, 160, 96), (2048, 1536, 512), (77, 112, 80)])
 def test_tcgen05_prompt_gated_epilogue(M, inter, K):
     """The prompt kernel with SiLU and gating in its epilogue equals product + silu_mul, bit for bit."""
