@@ -70,7 +70,9 @@ def cases():
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_config_golden.py REFERENCE_CHECKOUT")
+    ref = sys.argv[1]
     with tempfile.TemporaryDirectory() as tmp:
         exe = os.path.join(tmp, "config_probe")
         subprocess.run(["g++", "-std=c++17", "-O1", "-I", os.path.join(ref, "include"),
