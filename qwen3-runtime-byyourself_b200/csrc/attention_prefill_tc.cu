@@ -5,8 +5,11 @@
 // Same math as the reference's kernel (src/ops/gqa_attention.cu:84-153: causal by bound, scale
 // after the dot, online softmax and weighted sum in 32-bit), arranged for Blackwell:
 //   grid (tile of 128 new tokens, query head, sequence); three roles per block
-//   warp 0     TMA: the Q tile once, then one cache page (64 keys: K and V panels of the head's
-//              kv group, two 64-column halves each at head size 128) per stage of a ring
+//   warp 0     TMA: the Q tile once, then the K panels of the cache pages (64 keys of the head's kv
+//              group, two 64-column halves at head size 128) into a ring of three
+//   warp 6     TMA: the V panels into a ring of two.  K(j) is free again as soon as S(j) is done and
+//              V(j) only after O += P(j).V(j), so with rings of their own the K loads run two pages
+//              ahead of the products, which covers their latency at two blocks per SM
 //   warp 1     one thread issues the products: S(j) = Q.K_j^T into TMEM columns [0,64), then
 //              O += P_j.V_j with P read from TMEM and V as an MN-major shared-memory operand;
 //              S(j+1) is issued as soon as the softmax warps have read S(j)
@@ -29,12 +32,13 @@ namespace {
 constexpr int D = Q3_HEAD_DIM;
 static_assert(D == 64 || D == 128, "the tcgen05 attention takes head sizes 64 and 128");
 constexpr int PAGE = 64, BM = 128, HALVES = D / 64;
-constexpr int THREADS = 192;
-constexpr int STAGES = 2;
+constexpr int THREADS = 224;
+constexpr int K_STAGES = 3, V_STAGES = 2;                // pages of K and of V in flight or in use
 constexpr int Q_BYTES = HALVES * BM * 128;               // 128 rows x 128 bytes per half
 constexpr int PANEL_BYTES = HALVES * PAGE * 128;         // one page of K (or V): 64 keys x 128 bytes per half
-constexpr int STAGE_BYTES = 2 * PANEL_BYTES;
-constexpr int SMEM_BYTES = Q_BYTES + STAGES * STAGE_BYTES + 1024 + 256;
+// no slack for alignment: two blocks of head size 128 have to fit one SM, and the dynamic shared memory of
+// a kernel without static shared memory starts at a 1024-byte boundary (checked when the kernel starts)
+constexpr int SMEM_BYTES = Q_BYTES + (K_STAGES + V_STAGES) * PANEL_BYTES + 256;
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t COL_S = 0, COL_P = 64, COL_O = 128;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
@@ -126,6 +130,13 @@ constexpr uint32_t idesc(int m, int n, bool b_mn_major) {
            ((uint32_t)(m >> 4) << 24);
 }
 
+// 2^x by the special-function unit alone (-inf gives 0).
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -150,18 +161,27 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int rows = min(BM, n_new - tile * BM);
     const int n_pages = (pos0 + tile * BM + rows - 1) / PAGE + 1;        // pages 0 .. the one of the last row
 
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_smem = base, kv_smem = base + Q_BYTES;
-    const uint32_t bars = kv_smem + STAGES * STAGE_BYTES;
-    const uint32_t bar_q = bars, bar_kv_full = bars + 8, bar_kv_empty = bar_kv_full + 8 * STAGES;
-    const uint32_t bar_s_full = bar_kv_empty + 8 * STAGES, bar_s_read = bar_s_full + 8, bar_p_full = bar_s_read + 8;
+    const uint32_t base = smem_u32(smem_raw);
+    if (base & 1023u) {                                  // the swizzled tiles need 1024-byte alignment
+        if (threadIdx.x == 0) atomicExch(status, 18);
+        return;
+    }
+    const uint32_t q_smem = base, k_smem = base + Q_BYTES, v_smem = k_smem + K_STAGES * PANEL_BYTES;
+    const uint32_t bars = v_smem + V_STAGES * PANEL_BYTES;
+    const uint32_t bar_q = bars, bar_k_full = bars + 8, bar_k_empty = bar_k_full + 8 * K_STAGES;
+    const uint32_t bar_v_full = bar_k_empty + 8 * K_STAGES, bar_v_empty = bar_v_full + 8 * V_STAGES;
+    const uint32_t bar_s_full = bar_v_empty + 8 * V_STAGES, bar_s_read = bar_s_full + 8, bar_p_full = bar_s_read + 8;
     const uint32_t bar_pv_done = bar_p_full + 8, tmem_slot = bar_pv_done + 8;
 
     if (threadIdx.x == 0) {
         mbar_init(bar_q, 1);
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar_kv_full + 8 * s, 1);
-            mbar_init(bar_kv_empty + 8 * s, 1);
+        for (int s = 0; s < K_STAGES; ++s) {
+            mbar_init(bar_k_full + 8 * s, 1);
+            mbar_init(bar_k_empty + 8 * s, 1);
+        }
+        for (int s = 0; s < V_STAGES; ++s) {
+            mbar_init(bar_v_full + 8 * s, 1);
+            mbar_init(bar_v_empty + 8 * s, 1);
         }
         mbar_init(bar_s_full, 1);
         mbar_init(bar_s_read, 4);
@@ -180,22 +200,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem) : "r"(tmem_slot) : "memory");
 
     if (warp == 0) {
-        // ------------------------------------------------ TMA producer
+        // ------------------------------------------------ TMA producer: Q, then the K panels
         if (lane == 0) {
             mbar_expect_tx(bar_q, Q_BYTES);
 #pragma unroll
             for (int h = 0; h < HALVES; ++h) tma_load_2d(q_smem + h * BM * 128, &map_q, bar_q, head * D + h * 64, t0 + tile * BM);
             for (int j = 0; j < n_pages; ++j) {
-                const int s = j % STAGES;
-                if (!mbar_wait(bar_kv_empty + 8 * s, ((uint32_t)(j / STAGES) & 1u) ^ 1u)) { atomicExch(status, 11); break; }
-                const uint32_t k_dst = kv_smem + s * STAGE_BYTES, v_dst = k_dst + PANEL_BYTES;
+                const int s = j % K_STAGES;
+                if (!mbar_wait(bar_k_empty + 8 * s, ((uint32_t)(j / K_STAGES) & 1u) ^ 1u)) { atomicExch(status, 11); break; }
+                const uint32_t dst = k_smem + s * PANEL_BYTES;
                 const int row = (pages[j] * nkv + kvh) * PAGE;
-                mbar_expect_tx(bar_kv_full + 8 * s, STAGE_BYTES);
+                mbar_expect_tx(bar_k_full + 8 * s, PANEL_BYTES);
 #pragma unroll
-                for (int h = 0; h < HALVES; ++h) {
-                    tma_load_2d(k_dst + h * PAGE * 128, &map_k, bar_kv_full + 8 * s, h * 64, row);
-                    tma_load_2d(v_dst + h * PAGE * 128, &map_v, bar_kv_full + 8 * s, h * 64, row);
-                }
+                for (int h = 0; h < HALVES; ++h) tma_load_2d(dst + h * PAGE * 128, &map_k, bar_k_full + 8 * s, h * 64, row);
+            }
+        }
+    } else if (warp == 6) {
+        // ------------------------------------------------ TMA producer: the V panels
+        if (lane == 0) {
+            for (int j = 0; j < n_pages; ++j) {
+                const int s = j % V_STAGES;
+                if (!mbar_wait(bar_v_empty + 8 * s, ((uint32_t)(j / V_STAGES) & 1u) ^ 1u)) { atomicExch(status, 19); break; }
+                const uint32_t dst = v_smem + s * PANEL_BYTES;
+                const int row = (pages[j] * nkv + kvh) * PAGE;
+                mbar_expect_tx(bar_v_full + 8 * s, PANEL_BYTES);
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) tma_load_2d(dst + h * PAGE * 128, &map_v, bar_v_full + 8 * s, h * 64, row);
             }
         }
     } else if (warp == 1) {
@@ -203,15 +233,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         if (lane == 0) {
             constexpr uint32_t idesc_s = idesc(BM, PAGE, false), idesc_pv = idesc(BM, D, true);
             auto issue_s = [&](int j) {
-                const uint32_t k_src = kv_smem + (j % STAGES) * STAGE_BYTES;
+                const uint32_t k_src = k_smem + (j % K_STAGES) * PANEL_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * (BM * 128) + (kk & 3) * 32, koff = (kk >> 2) * (PAGE * 128) + (kk & 3) * 32;
                     tc_mma_ss(tmem + COL_S, desc_k_major(q_smem + off), desc_k_major(k_src + koff), idesc_s, kk > 0 ? 1u : 0u);
                 }
                 tc_commit(bar_s_full);
+                tc_commit(bar_k_empty + 8 * (j % K_STAGES));                 // the page's K is consumed
             };
-            bool ok = mbar_wait(bar_q, 0) && mbar_wait(bar_kv_full, 0);
+            bool ok = mbar_wait(bar_q, 0) && mbar_wait(bar_k_full, 0);
             if (!ok) atomicExch(status, 12);
             if (ok) {
                 tc_fence_after();
@@ -221,20 +252,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 // S(j+1) may overwrite the score columns once the softmax warps hold S(j) in registers
                 if (j + 1 < n_pages) {
                     ok = mbar_wait(bar_s_read, (uint32_t)j & 1u) &&
-                         mbar_wait(bar_kv_full + 8 * ((j + 1) % STAGES), (uint32_t)((j + 1) / STAGES) & 1u);
+                         mbar_wait(bar_k_full + 8 * ((j + 1) % K_STAGES), (uint32_t)((j + 1) / K_STAGES) & 1u);
                     if (!ok) { atomicExch(status, 13); break; }
                     tc_fence_after();
                     issue_s(j + 1);
                 }
-                ok = mbar_wait(bar_p_full, (uint32_t)j & 1u);                 // P(j) is in TMEM, O is rescaled
+                ok = mbar_wait(bar_p_full, (uint32_t)j & 1u) &&              // P(j) is in TMEM, O is rescaled
+                     mbar_wait(bar_v_full + 8 * (j % V_STAGES), (uint32_t)(j / V_STAGES) & 1u);
                 if (!ok) { atomicExch(status, 14); break; }
                 tc_fence_after();
-                const uint32_t v_src = kv_smem + (j % STAGES) * STAGE_BYTES + PANEL_BYTES;
+                const uint32_t v_src = v_smem + (j % V_STAGES) * PANEL_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < PAGE / 16; ++kk)
                     tc_mma_ts(tmem + COL_O, tmem + COL_P + kk * 8, desc_mn_major(v_src + kk * 16 * 128, PAGE * 128), idesc_pv,
                               (j > 0 || kk > 0) ? 1u : 0u);
-                tc_commit(bar_kv_empty + 8 * (j % STAGES));                   // the page's K and V are consumed
+                tc_commit(bar_v_empty + 8 * (j % V_STAGES));                 // the page's V is consumed
                 tc_commit(bar_pv_done);
             }
         }
@@ -259,31 +291,43 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             if (lane == 0) mbar_arrive(bar_s_read);
             const int key0 = j * PAGE;
             const bool edge = key0 + PAGE - 1 > pos0 + tile * BM;           // some key of the page lies after some row
-            float m_page = -INFINITY;
+            if (edge) {
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                float v = __uint_as_float(s[c]) * scale_log2;
-                if (edge && key0 + c > p_row) v = -INFINITY;
-                s[c] = __float_as_uint(v);
-                m_page = fmaxf(m_page, v);
+                for (int c = 0; c < 64; ++c)
+                    if (key0 + c > p_row) s[c] = 0xff800000u;                // -inf
             }
+            // the page's maximum on the raw dots (the scale is positive), four chains side by side
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 64; c += 4) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mx[e] = fmaxf(mx[e], __uint_as_float(s[c + e]));
+            }
+            const float m_page = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
             float alpha = 1.0f;
             bool raise = false;
             if (j == 0) {
                 m_run = m_page == -INFINITY ? 0.0f : m_page;                 // the first page overwrites O: nothing to rescale
             } else if (m_page > m_run + RESCALE_THRESHOLD) {
-                alpha = exp2f(m_run - m_page);
+                alpha = ex2_approx(m_run - m_page);
                 m_run = m_page;
                 raise = true;
             }
-            float sum = 0.0f;
+            // p = 2^(dot * scale - m): one multiply-add and one ex2 per score, four sums side by side
+            const float neg_m = -m_run;
+            float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             uint32_t p[32];
 #pragma unroll
-            for (int c = 0; c < 64; c += 2) {
-                const float a = exp2f(__uint_as_float(s[c]) - m_run), b = exp2f(__uint_as_float(s[c + 1]) - m_run);
-                sum += a + b;
+            for (int c = 0; c < 64; c += 4) {
+                const float a = ex2_approx(fmaf(__uint_as_float(s[c]), scale_log2, neg_m));
+                const float b = ex2_approx(fmaf(__uint_as_float(s[c + 1]), scale_log2, neg_m));
+                const float e = ex2_approx(fmaf(__uint_as_float(s[c + 2]), scale_log2, neg_m));
+                const float f = ex2_approx(fmaf(__uint_as_float(s[c + 3]), scale_log2, neg_m));
+                part[0] += a; part[1] += b; part[2] += e; part[3] += f;
                 p[c >> 1] = pack_bf16(a, b);
+                p[(c >> 1) + 1] = pack_bf16(e, f);
             }
+            const float sum = (part[0] + part[1]) + (part[2] + part[3]);
             l_run = l_run * alpha + sum;
             if (j > 0) {
                 ok = mbar_wait(bar_pv_done, (uint32_t)(j - 1) & 1u);         // O and the P columns are free again
@@ -381,7 +425,7 @@ Q3_EXPORT int q3_attention_prefill_tc_bf16(const void* q, const void* k_pages, c
                                            int pages_per_seq, int n_seqs, int max_new, int64_t n_tokens,
                                            int64_t n_cache_pages, int nq, int nkv, float scale, int* status, void* stream) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
-    if (nq <= 0 || nkv <= 0 || nq % nkv != 0) return Q3_ERR_BAD_SIZE;
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || !(scale > 0.0f)) return Q3_ERR_BAD_SIZE;   // the row maximum is taken before scaling
     if (n_seqs > 65535 || nq > 65535) return Q3_ERR_TOO_LARGE;
     if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(out)) return Q3_ERR_MISALIGNED;
     static bool configured = false;

@@ -136,7 +136,7 @@ def _prefill_flash_kernel(part, q, cache, out, ctx, table) -> bool:
 def _prefill_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
     """Both products of the attention on tcgen05 with TMA-fed tiles: head sizes 64 and 128, no window,
     and enough new tokens for 128-row tiles to be worth it."""
-    if not ops.attention_prefill_tc_fits(part.head_dim, part.window) or ctx.max_new < tc_prefill_rows:
+    if not ops.attention_prefill_tc_fits(part.head_dim, part.window) or ctx.max_new < tc_prefill_rows or part.scale <= 0:
         return False
     ops.attention_prefill_tc(q[:ctx.n_tokens], cache.keys, cache.values, out, ctx.seq_start, ctx.seq_pos0, table,
                              ctx.n_seqs, ctx.max_new, ctx.n_tokens, part.num_heads, part.num_kv_heads, part.head_dim,

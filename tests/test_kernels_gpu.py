@@ -587,7 +587,7 @@ def test_tcgen05_prompt_gated_epilogue(M, inter, K):
     assert np.max(np.abs(back(fused) - want)) <= 2e-2 * max(1.0, float(np.abs(want).max()))
 
 
-@pytest.mark.parametrize("nq,nkv,d", [(8, 2, 128), (4, 4, 64), (6, 1, 128)])
+@pytest.mark.parametrize("nq,nkv,d", [(8, 2, 128), (4, 4, 64), (6, 1, 128), (4, 2, 64)])
 def test_prefill_attention_tcgen05_kernel(nq, nkv, d):
     """The TMA + tcgen05 attention: prompts of unequal length in one launch, then a second launch
     that continues them from the cache, over shuffled pages, against float64 causal attention.
