@@ -82,8 +82,27 @@ def _check(code: int, name: str):
         raise KernelError(f"{name}: {what}")
 
 
+_pinned_stream: Optional[int] = None
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    return _pinned_stream if _pinned_stream is not None else torch.cuda.current_stream().cuda_stream
+
+
+class on_current_stream:
+    """Within this scope every launch goes to the stream that is current on entry, looked up once
+    (asking torch for the current stream costs more than a launch)."""
+
+    def __enter__(self):
+        global _pinned_stream
+        self._before = _pinned_stream
+        _pinned_stream = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _pinned_stream
+        _pinned_stream = self._before
+        return False
 
 
 def _dev(t: torch.Tensor, name: str, dtype=None):

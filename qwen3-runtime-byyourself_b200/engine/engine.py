@@ -201,7 +201,8 @@ class _DecodeGraph:
         from ..csrc import ops
         model, cache = self.engine.model, self.engine.cache
         self._fill([], [], [])
-        model.forward(self.ctx, cache)               # loads kernels and library handles outside the capture
+        with ops.on_current_stream():
+            model.forward(self.ctx, cache)           # loads kernels and library handles outside the capture
         torch.cuda.synchronize(self.engine.device)
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
@@ -211,7 +212,8 @@ class _DecodeGraph:
         gc.disable()
         try:
             with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                self.logits = model.forward(self.ctx, cache)
+                with ops.on_current_stream():        # the capture's own stream
+                    self.logits = model.forward(self.ctx, cache)
         finally:
             if gc_was_enabled:
                 gc.enable()
@@ -338,7 +340,8 @@ class Engine:
             ctx = self._build_context(slots, n_new, pos0, token_ids, want_rows)
             if device_tokens is not None:
                 ctx.token_ids[:len(slots)].copy_(device_tokens)
-            logits = self.model.forward(ctx, self.cache)
+            with ops.on_current_stream():
+                logits = self.model.forward(ctx, self.cache)
             self.launches += ops.launch_count() - before
         self.cache.commit(step)
         return logits
