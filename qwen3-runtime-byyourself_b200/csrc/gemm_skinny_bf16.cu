@@ -185,9 +185,12 @@ int dispatch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, cudaStr
     if (K <= 0 || K % 8 != 0 || M > 64 || (GATED && N % 16 != 0)) return Q3_ERR_BAD_SIZE;
     if (!aligned16(X) || !aligned16(W)) return Q3_ERR_MISALIGNED;
     const bool few_rows = (N + 15) / 16 <= 296;
-    if (M <= 8)
-        return few_rows ? launch<1, 1, 16, 2, 2, GATED, OutT>(X, W, Y, M, N, K, stream)
-                        : launch<1, 1, 8, 4, 3, GATED, OutT>(X, W, Y, M, N, K, stream);
+    if (M <= 8) {
+        if (few_rows) return launch<1, 1, 16, 2, 2, GATED, OutT>(X, W, Y, M, N, K, stream);
+        // one wave of three blocks per SM: two k-blocks in flight per warp measured a little faster than four
+        if ((N + 15) / 16 <= 444) return launch<1, 1, 8, 2, 3, GATED, OutT>(X, W, Y, M, N, K, stream);
+        return launch<1, 1, 8, 4, 3, GATED, OutT>(X, W, Y, M, N, K, stream);
+    }
     if (M <= 16)
         return few_rows ? launch<2, 1, 16, 2, 1, GATED, OutT>(X, W, Y, M, N, K, stream)
                         : launch<2, 1, 8, 2, 3, GATED, OutT>(X, W, Y, M, N, K, stream);
