@@ -50,6 +50,7 @@ class StepContext:
     seq_start: torch.Tensor       # [B + 1] int32: first packed token of each sequence
     seq_pos0: torch.Tensor        # [B] int32: tokens already cached before the step
     want_rows: torch.Tensor       # [R] int32: packed token rows whose logits are wanted
+    want_all: bool = False        # every packed row is wanted, in order (R == N): nothing to gather
     page_tables: List[torch.Tensor] = field(default_factory=list)   # per cache group [B, pages_per_slot] int32
     host_slots: List[int] = field(default_factory=list)
     host_n_new: List[int] = field(default_factory=list)

@@ -103,12 +103,12 @@ class _MetaBuffer:
 
 
 def context_views(cache, dev, lay, N, B, R, scratch, dtype, max_positions, is_decode, max_new, max_context,
-                  host=None) -> StepContext:
+                  host=None, want_all=False) -> StepContext:
     """A StepContext whose device fields are views of the metadata buffer `dev` laid out by `lay`."""
     G, P = len(cache.groups), cache.pages_per_slot
     return StepContext(
-        n_tokens=N, n_seqs=B, n_want=R, is_decode=is_decode, max_new=max_new, max_context=max_context,
-        max_positions=max_positions, dtype=dtype, device=dev.device, scratch=scratch,
+        n_tokens=N, n_seqs=B, n_want=R, want_all=want_all, is_decode=is_decode, max_new=max_new,
+        max_context=max_context, max_positions=max_positions, dtype=dtype, device=dev.device, scratch=scratch,
         token_ids=dev[lay.token_ids:lay.token_ids + N], token_seq=dev[lay.token_seq:lay.token_seq + N],
         token_pos=dev[lay.token_pos:lay.token_pos + N], seq_slots=dev[lay.seq_slots:lay.seq_slots + B],
         seq_start=dev[lay.seq_start:lay.seq_start + B + 1], seq_pos0=dev[lay.seq_pos0:lay.seq_pos0 + B],
@@ -143,7 +143,8 @@ def build_context(cache, meta: "_MetaBuffer", scratch, dtype, max_positions, slo
         host[lay.tables[g]:lay.tables[g] + B * P] = cache.page_rows(g, slots).reshape(-1)
     meta.upload(lay.total)
     return context_views(cache, meta.dev, lay, N, B, R, scratch, dtype, max_positions, bool(n_new_a.max() == 1),
-                         int(n_new_a.max()), int((pos0_a + n_new_a).max()), host=(slots, n_new, pos0))
+                         int(n_new_a.max()), int((pos0_a + n_new_a).max()), host=(slots, n_new, pos0),
+                         want_all=(R == N and list(want_rows) == list(range(N))))
 
 
 def decode_bucket(n: int) -> int:
@@ -170,7 +171,8 @@ class _DecodeGraph:
         self.meta.reserve(self.layout.total)
         self.scratch = Scratch(engine.device)
         self.ctx = context_views(cache, self.meta.dev, self.layout, rows, rows, rows, self.scratch, engine.dtype,
-                                 engine.max_seq_len, is_decode=True, max_new=1, max_context=engine.max_seq_len)
+                                 engine.max_seq_len, is_decode=True, max_new=1, max_context=engine.max_seq_len,
+                                 want_all=True)
         self.graph = None
         self.logits = None
         self.launches = 0

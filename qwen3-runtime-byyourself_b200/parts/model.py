@@ -97,10 +97,13 @@ class Model:
         if ctx.n_want == 0:
             return None
         R = ctx.n_want
-        rows = ctx.scratch.get("model.rows", (R, H), ctx.dtype)
-        ops.gather_rows(residual, ctx.want_rows[:R], rows, delta)
         normed = ctx.scratch.get("model.rows_normed", (R, H), ctx.dtype)
-        self.final_norm(rows, normed)
+        if ctx.want_all:                                   # a decode step: the last residual sum rides in the norm
+            self.final_norm(residual, normed, delta)
+        else:
+            rows = ctx.scratch.get("model.rows", (R, H), ctx.dtype)
+            ops.gather_rows(residual, ctx.want_rows[:R], rows, delta)
+            self.final_norm(rows, normed)
         logits = ctx.scratch.get("model.logits", (R, self.plan.vocab_size), torch.float32)
         return self.head.forward(normed, logits)
 
