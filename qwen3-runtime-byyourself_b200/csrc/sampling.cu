@@ -19,6 +19,8 @@
 // The uniform number is not the reference's shared mt19937_64 stream (which makes a
 // sequence's tokens depend on what else is in the batch): it is a hash of (seed,
 // sequence id, step), so every sequence has a stream of its own.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
@@ -95,23 +97,42 @@ struct Selected {
     uint64_t inside;   // weight (or count) of the run of `key`
 };
 
+constexpr int S_THREADS = 1024;   // threads of the sampling kernel
+constexpr int SHORT_LIST = 1024;  // candidates that are sorted in shared memory instead of selected by radix
+
+constexpr int PRIVATE_BYTES = 32 * 1024;   // private histograms of the warps (dynamic shared memory)
+
 // Finds the key at which the cumulative sum, taken from the highest key downwards,
 // first reaches `threshold` (1 <= threshold <= sum over all candidates).  WEIGHTED:
 // sums fixed-point weights of the candidates (key >= floor_key); otherwise counts all.
+// Most logits share their high bits, so one histogram for the block would be thousands of
+// atomics on one address: every warp (every pair of warps for the 64-bit sums) counts into
+// a histogram of its own in `priv`, and the histograms are added up afterwards.
 template <bool WEIGHTED>
 __device__ Selected radix_select(const float* __restrict__ x, int valid, uint64_t threshold, uint32_t floor_key,
-                                 double temperature, double max_score, unsigned long long* hist, uint64_t* bcast) {
+                                 double temperature, double max_score, unsigned long long* hist, uint64_t* bcast,
+                                 void* priv) {
+    using Word = typename std::conditional<WEIGHTED, unsigned long long, unsigned int>::type;
+    constexpr int COPIES = PRIVATE_BYTES / (256 * (int)sizeof(Word));      // 32 or 16
+    Word* mine = reinterpret_cast<Word*>(priv) + ((threadIdx.x >> 5) % COPIES) * 256;
     uint32_t prefix = 0, mask = 0;
     uint64_t before = 0, inside = 0;
     for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int b = threadIdx.x; b < 256; b += THREADS) hist[b] = 0ull;
+        for (int b = threadIdx.x; b < COPIES * 256; b += S_THREADS) reinterpret_cast<Word*>(priv)[b] = 0;
         __syncthreads();
-        for (int i = threadIdx.x; i < valid; i += THREADS) {
+        for (int i = threadIdx.x; i < valid; i += S_THREADS) {
             const float v = x[i];
             const uint32_t key = float_key(v);
             if ((key & mask) != prefix || key < floor_key) continue;
-            const unsigned long long add = WEIGHTED ? fixed_weight(v, temperature, max_score) : 1ull;
-            if (add) atomicAdd(&hist[(key >> shift) & 255u], add);
+            const Word add = WEIGHTED ? (Word)fixed_weight(v, temperature, max_score) : (Word)1;
+            if (add) atomicAdd(&mine[(key >> shift) & 255u], add);
+        }
+        __syncthreads();
+        for (int b = threadIdx.x; b < 256; b += S_THREADS) {
+            unsigned long long sum = 0ull;
+#pragma unroll 4
+            for (int c = 0; c < COPIES; ++c) sum += reinterpret_cast<Word*>(priv)[c * 256 + b];
+            hist[b] = sum;
         }
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -142,16 +163,26 @@ __device__ Selected radix_select(const float* __restrict__ x, int valid, uint64_
     return Selected{prefix, before, inside};
 }
 
-__global__ void __launch_bounds__(THREADS)
+// The uniform number of a row: a hash of (seed, sequence id, step), 53 bits.
+__device__ __forceinline__ double uniform_of(uint64_t seed, int64_t seq_id, int step) {
+    const uint64_t h = splitmix64(splitmix64(seed ^ splitmix64((uint64_t)seq_id)) + (uint64_t)step);
+    return (double)(h >> 11) * (1.0 / 9007199254740992.0);
+}
+
+__global__ void __launch_bounds__(S_THREADS)
 sample_kernel(const float* __restrict__ logits, int64_t stride, int valid, float temperature_f, int top_k, float top_p,
               uint64_t seed, const int64_t* __restrict__ seq_ids, const int* __restrict__ steps,
               int* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char private_histograms[];   // PRIVATE_BYTES
     __shared__ unsigned long long hist[256];
     __shared__ uint64_t bcast[3];
     __shared__ float red[33];
     __shared__ unsigned long long total_s;
-    __shared__ int counts[THREADS];
+    __shared__ int counts[S_THREADS];
     __shared__ int found[2];
+    __shared__ unsigned long long list[SHORT_LIST];      // (key << 32) | ~id, then cumulative weights
+    __shared__ int list_id[SHORT_LIST];
+    __shared__ int n_list;
     pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
@@ -160,7 +191,7 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int valid, float
     // the maximum, and a refusal of rows with NaN or Inf (the reference throws there)
     float mx = -INFINITY;
     int bad = 0;
-    for (int i = tid; i < valid; i += THREADS) {
+    for (int i = tid; i < valid; i += S_THREADS) {
         const float v = x[i];
         if (!isfinite(v)) bad = 1;
         mx = fmaxf(mx, v);
@@ -170,21 +201,114 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int valid, float
         if (tid == 0) out[row] = -1;
         return;
     }
+    const float thread_max = mx;
     mx = block_max(mx, red);
     const double temperature = (double)temperature_f;
     const double max_score = (double)mx / temperature;
+    const double u = uniform_of(seed, seq_ids[row], steps[row]);
+
+    // bitonic sort of the 1024 words of `list`, descending: one element a thread
+    auto sort_list = [&]() {
+        for (int size = 2; size <= SHORT_LIST; size <<= 1) {
+            for (int gap = size >> 1; gap > 0; gap >>= 1) {
+                const int other = tid ^ gap;
+                if (other > tid) {
+                    const unsigned long long a = list[tid], b = list[other];
+                    const bool descending = (tid & size) == 0;
+                    if ((a < b) == descending) { list[tid] = b; list[other] = a; }
+                }
+                __syncthreads();
+            }
+        }
+    };
+    // every logit whose key reaches `floor` goes to `list` as (key << 32) | ~id; returns how many there are
+    auto gather = [&](uint32_t floor) {
+        if (tid == 0) n_list = 0;
+        list[tid] = 0ull;                                                // padding sorts to the end
+        __syncthreads();
+        for (int i = tid; i < valid; i += S_THREADS) {
+            const uint32_t key = float_key(x[i]);
+            if (key >= floor) {
+                const int at = atomicAdd(&n_list, 1);
+                if (at < SHORT_LIST) list[at] = ((unsigned long long)key << 32) | (uint32_t)(~(uint32_t)i);
+            }
+        }
+        __syncthreads();
+        return n_list;
+    };
 
     // top-k: the k-th best key; every key that reaches it stays
     uint32_t floor_key = 0;
-    if (top_k > 0 && top_k < valid) {
-        floor_key = radix_select<false>(x, valid, (uint64_t)top_k, 0u, temperature, max_score, hist, bcast).key;
+    uint64_t n_candidates = (uint64_t)valid;
+    bool listed = false;                                                 // the candidates stand sorted in `list`
+    if (top_k > 0 && top_k < valid && top_k <= S_THREADS) {
+        // The k-th best of the threads' own maxima is a lower bound of the k-th best logit (k logits reach
+        // it), so what reaches that bound holds every candidate, ties included, and is usually a short list.
+        list[tid] = thread_max == -INFINITY ? 0ull : (unsigned long long)float_key(thread_max);
+        __syncthreads();
+        sort_list();
+        const uint32_t bound = (uint32_t)list[top_k - 1];
+        __syncthreads();
+        if (bound != 0u && gather(bound) <= SHORT_LIST) {
+            sort_list();
+            floor_key = (uint32_t)(list[top_k - 1] >> 32);
+            if (tid < SHORT_LIST && (uint32_t)(list[tid] >> 32) >= floor_key &&
+                (tid + 1 == SHORT_LIST || (uint32_t)(list[tid + 1] >> 32) < floor_key))
+                found[1] = tid + 1;                                      // keys fall along the list: one thread sees the edge
+            __syncthreads();
+            n_candidates = (uint64_t)found[1];
+            listed = true;
+        }
+    }
+    if (!listed && top_k > 0 && top_k < valid) {
+        const Selected kth = radix_select<false>(x, valid, (uint64_t)top_k, 0u, temperature, max_score, hist, bcast, private_histograms);
+        floor_key = kth.key;
+        n_candidates = kth.before + kth.inside;
     }
 
+    if (n_candidates <= (uint64_t)SHORT_LIST) {
+        // ---- few candidates: order them as the reference does (score down, then id up) and walk the sums
+        if (!listed) {
+            gather(floor_key);
+            sort_list();
+        }
+        const int n = (int)n_candidates;
+        // weights, then their running sums in order (Hillis-Steele over 1024 words)
+        unsigned long long w = 0ull;
+        if (tid < n) {
+            const unsigned long long e = list[tid];
+            list_id[tid] = (int)(~(uint32_t)e);
+            w = fixed_weight(key_float((uint32_t)(e >> 32)), temperature, max_score);
+        }
+        __syncthreads();
+        list[tid] = w;
+        __syncthreads();
+        for (int off = 1; off < SHORT_LIST; off <<= 1) {
+            const unsigned long long add = tid >= off ? list[tid - off] : 0ull;
+            __syncthreads();
+            list[tid] += add;
+            __syncthreads();
+        }
+        const uint64_t total = list[n - 1];                              // >= 2^40: the maximum itself has weight one
+        uint64_t cut = (uint64_t)ceil((double)top_p * (double)total);
+        cut = cut < 1 ? 1 : (cut > total ? total : cut);
+        // top-p: the shortest prefix whose weight reaches the cut
+        if (tid < n && list[tid] >= cut && (tid == 0 || list[tid - 1] < cut)) found[0] = tid;
+        __syncthreads();
+        const uint64_t kept = list[found[0]];
+        uint64_t r = (uint64_t)(u * (double)kept);
+        if (r >= kept) r = kept - 1;
+        // the draw: the first candidate whose cumulative weight exceeds r (it lies inside the kept prefix)
+        if (tid < n && list[tid] > r && (tid == 0 || list[tid - 1] <= r)) out[row] = list_id[tid];
+        return;
+    }
+
+    // ---- many candidates (no top-k, or a long run of equal logits at its edge): selection by radix
     // total weight of the candidates
     if (tid == 0) total_s = 0ull;
     __syncthreads();
     unsigned long long part = 0ull;
-    for (int i = tid; i < valid; i += THREADS) {
+    for (int i = tid; i < valid; i += S_THREADS) {
         const float v = x[i];
         if (float_key(v) >= floor_key) part += fixed_weight(v, temperature, max_score);
     }
@@ -195,7 +319,7 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int valid, float
     // top-p: shortest prefix whose weight reaches top_p * total
     uint64_t cut = (uint64_t)ceil((double)top_p * (double)total);
     cut = cut < 1 ? 1 : (cut > total ? total : cut);
-    const Selected edge = radix_select<true>(x, valid, cut, floor_key, temperature, max_score, hist, bcast);
+    const Selected edge = radix_select<true>(x, valid, cut, floor_key, temperature, max_score, hist, bcast, private_histograms);
     const uint64_t edge_w = fixed_weight(key_float(edge.key), temperature, max_score);
     uint64_t edge_n = edge_w ? (cut - edge.before + edge_w - 1) / edge_w : 1;
     const uint64_t edge_count = edge_w ? edge.inside / edge_w : 1;
@@ -203,18 +327,16 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int valid, float
     const uint64_t kept = edge.before + edge_n * edge_w;
 
     // the draw: first candidate whose cumulative weight exceeds r = u * kept
-    const uint64_t h = splitmix64(splitmix64(seed ^ splitmix64((uint64_t)seq_ids[row])) + (uint64_t)steps[row]);
-    const double u = (double)(h >> 11) * (1.0 / 9007199254740992.0);
     uint64_t r = (uint64_t)(u * (double)kept);
     if (r >= kept) r = kept - 1;
-    const Selected hit = radix_select<true>(x, valid, r + 1, floor_key, temperature, max_score, hist, bcast);
+    const Selected hit = radix_select<true>(x, valid, r + 1, floor_key, temperature, max_score, hist, bcast, private_histograms);
     const uint64_t hit_w = fixed_weight(key_float(hit.key), temperature, max_score);
     const uint64_t hit_count = hit_w ? hit.inside / hit_w : 1;
     uint64_t nth = hit_w ? (r - hit.before) / hit_w : 0;  // 0-based place inside the run of equals
     if (nth >= hit_count) nth = hit_count - 1;
 
     // the nth lowest id among the logits equal to hit.key: contiguous id ranges per thread
-    const int chunk = (valid + THREADS - 1) / THREADS;
+    const int chunk = (valid + S_THREADS - 1) / S_THREADS;
     const int lo = tid * chunk, hi = min(valid, lo + chunk);
     int mine = 0;
     for (int i = lo; i < hi; ++i) mine += float_key(x[i]) == hit.key;
@@ -223,7 +345,7 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int valid, float
     if (tid == 0) {
         int64_t left = (int64_t)nth;
         int owner = -1, last_owner = -1;
-        for (int t = 0; t < THREADS; ++t) {
+        for (int t = 0; t < S_THREADS; ++t) {
             if (counts[t] == 0) continue;
             last_owner = t;
             if (left < counts[t]) { owner = t; break; }
@@ -265,6 +387,12 @@ Q3_EXPORT int q3_sample_f32(const float* logits, int64_t stride, int rows, int v
     if (rows <= 0) return 0;
     if (valid <= 0 || valid > stride || !(temperature > 0.0f) || top_k < 0 || !(top_p > 0.0f && top_p <= 1.0f))
         return Q3_ERR_BAD_SIZE;
-    return (int)q3_launch(sample_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, logits, stride, valid,
+    static bool configured = false;
+    if (!configured) {              // static and dynamic shared memory together pass the default limit of 48 KB
+        cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRIVATE_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    return (int)q3_launch(sample_kernel, dim3(rows), dim3(S_THREADS), PRIVATE_BYTES, (cudaStream_t)stream, logits, stride, valid,
                           temperature, top_k, top_p, seed, seq_ids, steps, out);
 }
