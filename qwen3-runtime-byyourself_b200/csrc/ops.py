@@ -261,14 +261,18 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, valid: Optional[int] = None)
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int,
-           seq_ids: torch.Tensor, steps: torch.Tensor, valid: Optional[int] = None) -> torch.Tensor:
-    """One draw per row; out[r] = -1 marks a row with a non-finite logit."""
+           seq_ids: torch.Tensor, steps, valid: Optional[int] = None) -> torch.Tensor:
+    """One draw per row; out[r] = -1 marks a row with a non-finite logit.  `steps` is an int32 tensor with
+    the step of every row, or one int for all rows."""
     rows, vocab = logits.shape
     fn = _fn("sampling.cu", "q3_sample_f32",
-             [c_void_p, c_int64, c_int, c_int, c_float, c_int, c_float, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p])
+             [c_void_p, c_int64, c_int, c_int, c_float, c_int, c_float, c_uint64, c_void_p, c_void_p, c_int, c_void_p,
+              c_void_p])
+    per_row = isinstance(steps, torch.Tensor)
     _check(fn(_dev(logits, "logits", torch.float32), vocab, rows, int(valid or vocab), float(temperature), int(top_k),
               float(top_p), int(seed) & 0xFFFFFFFFFFFFFFFF, _dev(seq_ids, "seq_ids", torch.int64),
-              _dev(steps, "steps", torch.int32), _dev(out, "out", torch.int32), _stream()), "sample")
+              _dev(steps, "steps", torch.int32) if per_row else None, 0 if per_row else int(steps),
+              _dev(out, "out", torch.int32), _stream()), "sample")
     return out
 
 

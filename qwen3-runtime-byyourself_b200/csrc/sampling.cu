@@ -171,7 +171,7 @@ __device__ __forceinline__ double uniform_of(uint64_t seed, int64_t seq_id, int 
 
 __global__ void __launch_bounds__(S_THREADS)
 sample_kernel(const float* __restrict__ logits, int64_t stride, int valid, float temperature_f, int top_k, float top_p,
-              uint64_t seed, const int64_t* __restrict__ seq_ids, const int* __restrict__ steps,
+              uint64_t seed, const int64_t* __restrict__ seq_ids, const int* __restrict__ steps, int step_all,
               int* __restrict__ out) {
     extern __shared__ __align__(16) unsigned char private_histograms[];   // PRIVATE_BYTES
     __shared__ unsigned long long hist[256];
@@ -205,7 +205,7 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int valid, float
     mx = block_max(mx, red);
     const double temperature = (double)temperature_f;
     const double max_score = (double)mx / temperature;
-    const double u = uniform_of(seed, seq_ids[row], steps[row]);
+    const double u = uniform_of(seed, seq_ids[row], steps != nullptr ? steps[row] : step_all);
 
     // bitonic sort of the 1024 words of `list`, descending: one element a thread
     auto sort_list = [&]() {
@@ -380,9 +380,9 @@ Q3_EXPORT int q3_argmax_f32(const float* logits, int64_t stride, int rows, int v
     return (int)q3_launch(argmax_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, logits, stride, valid, out);
 }
 
-// out[row] = -1 marks a row with a non-finite logit.
+// out[row] = -1 marks a row with a non-finite logit.  `steps` may be null: every row is then at step `step_all`.
 Q3_EXPORT int q3_sample_f32(const float* logits, int64_t stride, int rows, int valid, float temperature, int top_k,
-                            float top_p, uint64_t seed, const int64_t* seq_ids, const int* steps, int* out,
+                            float top_p, uint64_t seed, const int64_t* seq_ids, const int* steps, int step_all, int* out,
                             void* stream) {
     if (rows <= 0) return 0;
     if (valid <= 0 || valid > stride || !(temperature > 0.0f) || top_k < 0 || !(top_p > 0.0f && top_p <= 1.0f))
@@ -394,5 +394,5 @@ Q3_EXPORT int q3_sample_f32(const float* logits, int64_t stride, int rows, int v
         configured = true;
     }
     return (int)q3_launch(sample_kernel, dim3(rows), dim3(S_THREADS), PRIVATE_BYTES, (cudaStream_t)stream, logits, stride, valid,
-                          temperature, top_k, top_p, seed, seq_ids, steps, out);
+                          temperature, top_k, top_p, seed, seq_ids, steps, step_all, out);
 }

@@ -57,6 +57,7 @@ class Sampler:
         self._ids_hosts = [torch.empty(self._cap, dtype=torch.int64).pin_memory() for _ in range(2)]
         self._steps_hosts = [torch.empty(self._cap, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._out_host = torch.empty(self._cap, dtype=torch.int32).pin_memory()
+        self._ids_on_device = [None, None]
 
     def choose_device(self, logits: torch.Tensor, sequence_ids: Sequence[int], steps: Sequence[int]) -> torch.Tensor:
         """int32 ids [rows] on the device; `sequence_ids[r]`/`steps[r]` key row r's random stream."""
@@ -67,13 +68,20 @@ class Sampler:
         if self.params.mode == "greedy":
             return ops.argmax(logits, out, valid)
         t = self._turn
-        self._ids_hosts[t][:rows] = torch.as_tensor(list(sequence_ids), dtype=torch.int64)
-        self._steps_hosts[t][:rows] = torch.as_tensor(list(steps), dtype=torch.int32)
-        self._ids_devs[t][:rows].copy_(self._ids_hosts[t][:rows], non_blocking=True)
-        self._steps_devs[t][:rows].copy_(self._steps_hosts[t][:rows], non_blocking=True)
+        ids_key = tuple(sequence_ids)
+        if self._ids_on_device[t] != ids_key:                # the same sequences as last time: nothing to upload
+            self._ids_hosts[t][:rows] = torch.as_tensor(ids_key, dtype=torch.int64)
+            self._ids_devs[t][:rows].copy_(self._ids_hosts[t][:rows], non_blocking=True)
+            self._ids_on_device[t] = ids_key
+        steps = list(steps)
+        if all(s == steps[0] for s in steps):                 # sequences that started together: one number
+            step_arg = int(steps[0])
+        else:
+            self._steps_hosts[t][:rows] = torch.as_tensor(steps, dtype=torch.int32)
+            self._steps_devs[t][:rows].copy_(self._steps_hosts[t][:rows], non_blocking=True)
+            step_arg = self._steps_devs[t][:rows]
         p = self.params
-        return ops.sample(logits, out, p.temperature, p.top_k, p.top_p, p.seed, self._ids_devs[t][:rows],
-                          self._steps_devs[t][:rows], valid)
+        return ops.sample(logits, out, p.temperature, p.top_k, p.top_p, p.seed, self._ids_devs[t][:rows], step_arg, valid)
 
     def choose_async(self, logits: torch.Tensor, sequence_ids: Sequence[int], steps: Sequence[int]) -> PendingChoice:
         """Start the choice and its copy to the host without waiting.  Two results can be in flight: the

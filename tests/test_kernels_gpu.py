@@ -292,6 +292,8 @@ def test_sampling_kernel_follows_the_reference_order(temperature, top_k, top_p, 
         want = [plain.sample_row(logits[r], np.float32(temperature), top_k, np.float32(top_p),
                                  uniform_for(seed, 100 + r, step), valid) for r in range(rows)]
         assert got == want, (step, got, want)
+    ops.sample(d, out, temperature, top_k, top_p, seed, seq_ids, 7, valid)       # one step number for all rows
+    assert out.tolist() == want
     bad = logits.copy()
     bad[2, 7] = np.inf
     ops.sample(torch.as_tensor(bad).cuda(), out, temperature, top_k, top_p, seed, seq_ids, steps, valid)
