@@ -50,13 +50,23 @@ __device__ __forceinline__ uint64_t fixed_weight(float logit, double temperature
     return (uint64_t)(w * FIX_ONE + 0.5);
 }
 
+constexpr int ARGMAX_BLOCKS = 8;   // blocks (one cluster) that share a row
+
+// A row is split over the blocks of a cluster; each finds the best of its share, and the block of
+// rank 0 picks among the shares through distributed shared memory.
 __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, int64_t stride, int valid, int* __restrict__ out) {
     __shared__ float best_v[THREADS / 32];
     __shared__ int best_i[THREADS / 32];
+    __shared__ float share_v;
+    __shared__ int share_i;
     pdl_launch_dependents();
     pdl_wait();
-    const float* x = logits + (int64_t)blockIdx.x * stride;
+    const int row = blockIdx.x / ARGMAX_BLOCKS, rank = blockIdx.x % ARGMAX_BLOCKS;
+    const float* x = logits + (int64_t)row * stride;
+    // shares of whole float4 packets, so that every share starts as aligned as the row does
+    const int per = (((valid + ARGMAX_BLOCKS - 1) / ARGMAX_BLOCKS) + 3) & ~3;
+    const int lo = min(valid, rank * per), hi = min(valid, lo + per);
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     auto take = [&](float v, int i) {
@@ -64,18 +74,19 @@ argmax_kernel(const float* __restrict__ logits, int64_t stride, int valid, int* 
         if (v > bv || bi == 0x7fffffff) { bv = v; bi = i; }
     };
     // a thread sees its indices in ascending order, so "greater, or the first" keeps the lowest id
-    int done = 0;
+    int done = lo;
     if ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
-        const int n4 = valid >> 2;
-        const float4* x4 = reinterpret_cast<const float4*>(x);
+        const int n4 = (hi - lo) >> 2;
+        const float4* x4 = reinterpret_cast<const float4*>(x + lo);
 #pragma unroll 4
         for (int i = threadIdx.x; i < n4; i += THREADS) {
             const float4 v = x4[i];
-            take(v.x, 4 * i); take(v.y, 4 * i + 1); take(v.z, 4 * i + 2); take(v.w, 4 * i + 3);
+            const int at = lo + 4 * i;
+            take(v.x, at); take(v.y, at + 1); take(v.z, at + 2); take(v.w, at + 3);
         }
-        done = n4 << 2;
+        done = lo + (n4 << 2);
     }
-    for (int i = done + threadIdx.x; i < valid; i += THREADS) take(x[i], i);
+    for (int i = done + threadIdx.x; i < hi; i += THREADS) take(x[i], i);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -87,8 +98,26 @@ argmax_kernel(const float* __restrict__ logits, int64_t stride, int valid, int* 
     if (threadIdx.x == 0) {
         for (int w = 1; w < THREADS / 32; ++w)
             if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) { bv = best_v[w]; bi = best_i[w]; }
-        out[blockIdx.x] = bi;
+        share_v = bv;
+        share_i = bi;
     }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (rank == 0 && threadIdx.x == 0) {
+        const uint32_t addr_v = (uint32_t)__cvta_generic_to_shared(&share_v), addr_i = (uint32_t)__cvta_generic_to_shared(&share_i);
+        for (uint32_t r = 1; r < (uint32_t)ARGMAX_BLOCKS; ++r) {         // an empty share holds (-inf, 0x7fffffff)
+            uint32_t remote_v, remote_i;
+            float ov;
+            int oi;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_v) : "r"(addr_v), "r"(r));
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_i) : "r"(addr_i), "r"(r));
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ov) : "r"(remote_v) : "memory");
+            asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(oi) : "r"(remote_i) : "memory");
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        out[row] = bi;
+    }
+    // nobody leaves while its share may still be read
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 struct Selected {
@@ -377,7 +406,9 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int valid, float
 Q3_EXPORT int q3_argmax_f32(const float* logits, int64_t stride, int rows, int valid, int* out, void* stream) {
     if (rows <= 0) return 0;
     if (valid <= 0 || valid > stride) return Q3_ERR_BAD_SIZE;
-    return (int)q3_launch(argmax_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, logits, stride, valid, out);
+    if ((int64_t)rows * ARGMAX_BLOCKS > 2147483647LL) return Q3_ERR_TOO_LARGE;
+    return (int)q3_launch_cluster(argmax_kernel, dim3(rows * ARGMAX_BLOCKS), dim3(THREADS), 0, (cudaStream_t)stream,
+                                  dim3(ARGMAX_BLOCKS, 1, 1), logits, stride, valid, out);
 }
 
 // out[row] = -1 marks a row with a non-finite logit.  `steps` may be null: every row is then at step `step_all`.
