@@ -294,6 +294,14 @@ def test_sampling_kernel_follows_the_reference_order(temperature, top_k, top_p, 
         assert got == want, (step, got, want)
     ops.sample(d, out, temperature, top_k, top_p, seed, seq_ids, 7, valid)       # one step number for all rows
     assert out.tolist() == want
+    # a row's draw does not depend on how many rows share the launch (the blocks per row do)
+    for part in (3, min(rows, 20)):
+        ops.sample(d[:part], out[:part], temperature, top_k, top_p, seed, seq_ids[:part], 7, valid)
+        assert out[:part].tolist() == want[:part]
+    many = d.repeat(10, 1)
+    out_many = torch.empty(many.shape[0], dtype=torch.int32, device="cuda")
+    ops.sample(many, out_many, temperature, top_k, top_p, seed, seq_ids.repeat(10), 7, valid)
+    assert out_many.tolist() == want * 10
     bad = logits.copy()
     bad[2, 7] = np.inf
     ops.sample(torch.as_tensor(bad).cuda(), out, temperature, top_k, top_p, seed, seq_ids, steps, valid)
