@@ -251,7 +251,8 @@ gemm_tcgen05_mid_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     }
     tc_fence_before();
     __syncwarp();
-    cluster_sync();                                                           // every block's partial tile is in place
+    if (ranks > 1) cluster_sync();                                            // every block's partial tile is in place
+    else __syncthreads();                                                     // (a block on its own: its own tile)
 
     // ---------------- reduce over the cluster: this block finishes the tokens m with m % ranks == rank
     pdl_wait();                                                               // no global write before this
@@ -297,7 +298,8 @@ gemm_tcgen05_mid_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         }
     }
     __syncwarp();
-    cluster_sync();                                                           // nobody leaves while its tile is being read
+    if (ranks > 1) cluster_sync();                                            // nobody leaves while its tile is being read
+    else __syncthreads();
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
