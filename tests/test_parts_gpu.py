@@ -465,3 +465,26 @@ def test_toy_routed_feed_forward_and_toy_position_encoding():
             for p in range(len(toks)):
                 if (rid, p) in got:
                     assert np.max(np.abs(got[(rid, p)] - want[p])) <= 1e-4, (rid, p)
+
+
+def test_linear_takes_every_form_of_the_product():
+    """`linear` chooses among the library's products by the shape: the few-row kernel, weights first (K split
+    over a cluster), tokens first on single SMs, tokens first on pairs of SMs, and the CUDA-core kernel for a
+    width that is no multiple of 8.  Every choice agrees with a 64-bit product of the same operands."""
+    from qwen3_b200.parts import linear as L
+    from qwen3_b200.csrc import ops
+    g = torch.Generator(device="cuda").manual_seed(3)
+    seen = set()
+    for M, N, K in [(3, 520, 256), (40, 520, 256), (128, 4096, 256), (384, 4096, 4096), (512, 4096, 4096),
+                    (700, 6144, 512), (1500, 512, 256), (2048, 2048, 2048), (300, 200, 100)]:
+        x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+        w = torch.randn(N, K, generator=g, device="cuda").to(torch.bfloat16)
+        for out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.full((M, N), float("nan"), dtype=out_dtype, device="cuda")
+            L.linear(x, w, out)
+            err = (out.double() - x.double() @ w.double().T).abs().max().item()
+            bound = 4e-5 * np.sqrt(K) * 4 if out_dtype == torch.float32 else 0.02 * np.sqrt(K)
+            assert err <= bound, (M, N, K, out_dtype, err)
+        seen.add("any_width" if K % 8 else "skinny" if M <= L.skinny_rows else L.tcgen05_form(M, N, K))
+    assert ops.tcgen05_status("cuda") == 0
+    assert seen == {"skinny", "weights_first", "prompt128", "pair", "any_width"}, seen
