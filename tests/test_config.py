@@ -27,6 +27,21 @@ def test_reference_fixture_0_6b_head_dim_is_not_hidden_over_heads():
     assert c.query_heads_per_kv_head == 2 and c.tie_word_embeddings is True
 
 
+@pytest.mark.parametrize("layers,hidden,heads,inter,params_b", [(40, 5120, 40, 17408, 14.77), (64, 5120, 64, 25600, 32.76)])
+def test_larger_shapes_of_the_family_parse_and_plan(layers, hidden, heads, inter, params_b):
+    """The 14B and 32B shapes (same keys as the 8B fixture, other sizes): derived sizes, the plan's tensor
+    list and its parameter count."""
+    with open(os.path.join(FIXTURES, "qwen3_8b.json")) as f:
+        root = json.load(f)
+    root.update(num_hidden_layers=layers, hidden_size=hidden, num_attention_heads=heads, intermediate_size=inter)
+    c = q.config_from_dict(root, strict=True)
+    assert (c.q_projection_size, c.kv_projection_size, c.query_heads_per_kv_head) == (heads * 128, 1024, heads // 8)
+    specs = q.build_model(c.plan()).weight_specs()
+    assert len(specs) == 2 + 11 * layers + 1                      # src/model/weights.cpp:83,123 (untied)
+    count = sum(int(__import__("math").prod(s.shape)) for s in specs.values())
+    assert abs(count / 1e9 - params_b) < 0.01
+
+
 def test_golden_accept_reject_matches_the_reference_parser():
     """tests/golden/config_cases.json was produced by the reference's own src/model/config.cpp
     compiled on the CPU (tests/golden/make_config_golden.py); both parsers must agree on every case."""
