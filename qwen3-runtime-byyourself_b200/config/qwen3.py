@@ -182,6 +182,24 @@ class Qwen3Config:
         config.validate()
         return config
 
+    @classmethod
+    def from_json(cls, path: str, strict: bool = False) -> "Qwen3Config":
+        """Read a config.json (or the folder that holds it) as this architecture's configuration."""
+        import json
+        import os
+        if os.path.isdir(path):
+            path = os.path.join(path, "config.json")
+        try:
+            with open(path, "r", encoding="utf-8") as f:
+                root = json.load(f)
+        except OSError as e:
+            raise ConfigError(f"cannot open model config: {path}: {e}") from None
+        except json.JSONDecodeError as e:
+            raise ConfigError(f"cannot parse model config {path!r}: {e}") from None
+        if not isinstance(root, dict):
+            raise ConfigError("model config root must be a JSON object")
+        return cls.from_dict(root, strict=strict)
+
     def validate(self) -> None:
         for key in ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
                     "num_attention_heads", "num_key_value_heads", "head_dim", "max_position_embeddings"):

@@ -21,6 +21,16 @@ def test_reference_fixture_8b():
     assert c.rope_theta == 1e6 and c.rms_norm_eps == 1e-6 and c.max_position_embeddings == 40960
 
 
+def test_from_json_reads_a_file_or_its_folder(tmp_path):
+    path = os.path.join(FIXTURES, "qwen3_8b.json")
+    assert q.Qwen3Config.from_json(path) == q.load_config(path)
+    with open(tmp_path / "config.json", "w") as f:
+        json.dump(tiny("A"), f)
+    assert q.Qwen3Config.from_json(str(tmp_path), strict=True) == q.config_from_dict(tiny("A"))
+    with pytest.raises(q.ConfigError):
+        q.Qwen3Config.from_json(str(tmp_path / "absent.json"))
+
+
 def test_reference_fixture_0_6b_head_dim_is_not_hidden_over_heads():
     c = q.load_config(os.path.join(FIXTURES, "qwen3_0_6b.json"))
     assert (c.hidden_size, c.num_hidden_layers, c.q_projection_size, c.kv_projection_size) == (1024, 28, 2048, 1024)
