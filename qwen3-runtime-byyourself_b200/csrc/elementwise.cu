@@ -110,44 +110,55 @@ __global__ void rms_norm_kernel(T* __restrict__ x, const T* __restrict__ delta, 
 
 // The same for rows that fit the registers of a block: every thread keeps PER packets of its row, so
 // the row is read once (twice with `delta`) and written once (twice); used for prompts, where the norms
-// are bound by memory traffic.
+// are bound by memory traffic.  A block walks rows (blockIdx.x, += gridDim.x) and asks for the packets
+// of its next row before it reduces the current one, so that loads are in flight across the barriers.
 template <typename T, int PER>
 __global__ void rms_norm_reg_kernel(T* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ w,
-                                    T* __restrict__ y, int size, float eps, int64_t x_stride, int64_t y_stride) {
+                                    T* __restrict__ y, int64_t rows, int size, float eps, int64_t x_stride,
+                                    int64_t y_stride) {
     constexpr int VEC = Pack<T>::N;
     __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
-    const int64_t row = blockIdx.x;
-    T* xr = x + row * x_stride;
-    const T* dr = delta ? delta + row * x_stride : nullptr;
-    T* yr = y + row * y_stride;
-    float v[PER][VEC];
-    float sq = 0.0f;
+    Pack<T> xin[PER], din[PER];
+    auto fetch = [&](int64_t row) {
 #pragma unroll
-    for (int p = 0; p < PER; ++p) {
-        const int c = (p * blockDim.x + threadIdx.x) * VEC;
-        if (c < size) {
-            load_vec<T, VEC>(xr + c, v[p]);
-            if (dr) {
-                float d[VEC];
-                load_vec<T, VEC>(dr + c, d);
-#pragma unroll
-                for (int i = 0; i < VEC; ++i) v[p][i] = round_to<T>(v[p][i] + d[i]);
-                store_vec<T, VEC>(xr + c, v[p]);
+        for (int p = 0; p < PER; ++p) {
+            const int c = (p * blockDim.x + threadIdx.x) * VEC;
+            if (c < size) {
+                xin[p] = load_pack<T>(x + row * x_stride + c);
+                if (delta) din[p] = load_pack<T>(delta + row * x_stride + c);
             }
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) sq += v[p][i] * v[p][i];
         }
-    }
-    const float inv = rsqrtf(block_sum(sq, scratch) / (float)size + eps);
+    };
+    int64_t row = blockIdx.x;
+    if (row < rows) fetch(row);
+    for (; row < rows; row += gridDim.x) {
+        T* xr = x + row * x_stride;
+        T* yr = y + row * y_stride;
+        float v[PER][VEC];
+        float sq = 0.0f;
 #pragma unroll
-    for (int p = 0; p < PER; ++p) {
-        const int c = (p * blockDim.x + threadIdx.x) * VEC;
-        if (c < size) {
+        for (int p = 0; p < PER; ++p) {
+            const int c = (p * blockDim.x + threadIdx.x) * VEC;
+            if (c < size) {
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) v[p][i] = round_to<T>(v[p][i] * inv) * w[c + i];
-            store_vec<T, VEC>(yr + c, v[p]);
+                for (int i = 0; i < VEC; ++i) v[p][i] = delta ? round_to<T>(xin[p].get(i) + din[p].get(i)) : xin[p].get(i);
+                if (delta) store_vec<T, VEC>(xr + c, v[p]);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) sq += v[p][i] * v[p][i];
+            }
+        }
+        if (row + gridDim.x < rows) fetch(row + gridDim.x);          // under the reduction and the stores below
+        const float inv = rsqrtf(block_sum(sq, scratch) / (float)size + eps);
+#pragma unroll
+        for (int p = 0; p < PER; ++p) {
+            const int c = (p * blockDim.x + threadIdx.x) * VEC;
+            if (c < size) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) v[p][i] = round_to<T>(v[p][i] * inv) * w[c + i];
+                store_vec<T, VEC>(yr + c, v[p]);
+            }
         }
     }
 }
@@ -164,15 +175,19 @@ static int rms_norm_launch(T* x, const T* delta, const float* w, T* y, int64_t r
         const int packs = size / V;
         const int per = (packs + 255) / 256;                       // packets a thread keeps
         const int threads = ((packs + per - 1) / per + 31) / 32 * 32;
-        if (per == 1)
-            return (int)q3_launch(rms_norm_reg_kernel<T, 1>, dim3((unsigned)rows), dim3(threads), 0, stream, x, delta, w, y,
-                                  size, eps, x_stride, y_stride);
-        if (per == 2)
-            return (int)q3_launch(rms_norm_reg_kernel<T, 2>, dim3((unsigned)rows), dim3(threads), 0, stream, x, delta, w, y,
-                                  size, eps, x_stride, y_stride);
-        if (per <= 4)
-            return (int)q3_launch(rms_norm_reg_kernel<T, 4>, dim3((unsigned)rows), dim3(threads), 0, stream, x, delta, w, y,
-                                  size, eps, x_stride, y_stride);
+        auto launch = [&](auto kernel) {
+            int sms = 0, device = 0, per_sm = 0;                      // blocks the GPU holds at once
+            cudaGetDevice(&device);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0);
+            const int64_t resident = (int64_t)(sms > 0 ? sms : 1) * (per_sm > 0 ? per_sm : 1);
+            const unsigned blocks = (unsigned)(rows < resident ? rows : resident);
+            return (int)q3_launch(kernel, dim3(blocks), dim3(threads), 0, stream, x, delta, w, y, rows, size, eps, x_stride,
+                                  y_stride);
+        };
+        if (per == 1) return launch(rms_norm_reg_kernel<T, 1>);
+        if (per == 2) return launch(rms_norm_reg_kernel<T, 2>);
+        if (per <= 4) return launch(rms_norm_reg_kernel<T, 4>);
     }
     const int per = vec ? V : 1;
     int threads = (size / per + 31) / 32 * 32;
