@@ -50,17 +50,40 @@ SHAPES = {
 PREFILL_TOKENS = 2048
 
 
+def _number_under(raw, key):
+    """The number stored under `key` in a JSON object, at the top or nested; a value that is itself an
+    object is read through its 'value', 'median' or 'mean'."""
+    if isinstance(raw, dict):
+        if key in raw:
+            v = raw[key]
+            if isinstance(v, dict):
+                for inner in ("value", "median", "mean"):
+                    if isinstance(v.get(inner), (int, float)):
+                        return float(v[inner])
+            elif isinstance(v, (int, float)) and not isinstance(v, bool):
+                return float(v)
+        for v in raw.values():
+            found = _number_under(v, key)
+            if found is not None:
+                return found
+    return None
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
         with open(path) as f:
             raw = json.load(f)
-        peaks = {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]), "source": "measured"}
-        if "bf16_tflops_sustained" in raw:
-            peaks["bf16_tflops_sustained"] = float(raw["bf16_tflops_sustained"])
-        return peaks
-    except (OSError, KeyError, ValueError, TypeError):
+    except (OSError, ValueError):
         return dict(FALLBACK_PEAKS)
+    hbm, flops = _number_under(raw, "hbm_gbs"), _number_under(raw, "bf16_tflops")
+    if not hbm or not flops:
+        return dict(FALLBACK_PEAKS)
+    peaks = {"hbm_gbs": hbm, "bf16_tflops": flops, "source": "measured"}
+    sustained = _number_under(raw, "bf16_tflops_sustained")
+    if sustained:
+        peaks["bf16_tflops_sustained"] = sustained
+    return peaks
 
 
 class ClockSampler:
