@@ -35,13 +35,16 @@ class GenerationOptions:
 
 def generate_token_ids(engine: Engine, prompts: Sequence[Sequence[int]], sampling: Optional[SamplingParams] = None,
                        options: Optional[GenerationOptions] = None, batch_size: Optional[int] = None,
-                       on_token=None) -> List[GenerationResult]:
-    """Generate for every prompt (token ids in, new token ids out) on `engine`."""
+                       on_token=None, sequence_ids: Optional[Sequence[int]] = None) -> List[GenerationResult]:
+    """Generate for every prompt (token ids in, new token ids out) on `engine`.  `sequence_ids` names the
+    requests to the sampler (default: their index); a request draws the same tokens under the same name
+    whatever else is in the batch."""
     from .sampling.sampler import Sampler
     sampling = sampling or SamplingParams()
     options = options or GenerationOptions()
     sampler = Sampler(sampling, engine.vocab_size, engine.device)
-    return generate(engine, prompts, sampler, options.max_new_tokens, options.stop_token_ids, batch_size, on_token)
+    return generate(engine, prompts, sampler, options.max_new_tokens, options.stop_token_ids, batch_size, on_token,
+                    sequence_ids)
 
 
 __all__ = [

@@ -79,7 +79,6 @@ decode_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                     const int* __restrict__ token_pos, const int* __restrict__ page_table, int pages_per_seq, int nq,
                     int nkv, float scale_log2, int window) {
     extern __shared__ __align__(16) unsigned char smem[];
-    pdl_launch_dependents();
     pdl_wait();
     const int split = blockIdx.x, n_splits = gridDim.x, kvh = blockIdx.y, t = blockIdx.z;
     const int G = nq / nkv;
@@ -202,6 +201,7 @@ decode_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         }
     }
     cp_async_wait<0>();
+    pdl_launch_dependents();   // the cache has been read: the next kernel may start and fetch its weights
     __syncthreads();     // every warp is done with the pipeline buffers: reuse them for the merge
 
     // merge the four warps: sm_o[warp][row][D], sm_ml[warp][row][2]

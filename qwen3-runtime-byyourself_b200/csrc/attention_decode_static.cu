@@ -4,6 +4,9 @@
 // this file instead of a buffer from the caller.
 #include <stdio.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "attention_decode.cu"
 #include "attention_decode_static.h"
 
@@ -15,19 +18,33 @@ static __device__ __align__(256) float g_static_scratch[Q3_DECODE_STATIC_MAX_FLO
 
 constexpr int MAX_DEVICES = 64;
 float* g_scratch_address[MAX_DEVICES];      // device address of the array, per device, once looked up
-bool g_device_ready[MAX_DEVICES];
+std::atomic<bool> g_device_ready[MAX_DEVICES];
+std::mutex g_prepare_mutex;
 
 // First call on the current device: find the array's device address and raise the kernel's
-// shared-memory limit.  Neither allocates.  Not meant to run under stream capture.
+// shared-memory limit.  Neither allocates.  Not meant to run under stream capture.  Host threads
+// that make their first call at the same time take turns here; the flag is published last.
 int prepare_device(int device) {
+    std::lock_guard<std::mutex> lock(g_prepare_mutex);
+    if (g_device_ready[device].load(std::memory_order_acquire)) return 0;
     float* address = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&address, g_static_scratch);
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     g_scratch_address[device] = address;
-    g_device_ready[device] = true;
+    g_device_ready[device].store(true, std::memory_order_release);
     return 0;
+}
+
+// n_tokens * nq * n_splits * (D + 2) <= limit, checked factor by factor so that no product can wrap.
+bool fits_static_scratch(int64_t n_tokens, int nq, int n_splits) {
+    int64_t room = Q3_DECODE_STATIC_MAX_FLOATS / (D + 2);
+    if (n_tokens > room) return false;
+    room /= n_tokens;
+    if (nq > room) return false;
+    room /= nq;
+    return n_splits <= room;
 }
 
 }  // namespace
@@ -38,21 +55,20 @@ Q3_EXPORT int q3_attention_decode_bf16_static(const void* q, const void* k_pages
                                               int window, int n_splits, void* stream_) {
     if (n_tokens <= 0) return 0;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || n_splits <= 0) return Q3_ERR_BAD_SIZE;
-    if (n_tokens > 65535 || nkv > 65535) return Q3_ERR_TOO_LARGE;
-    const int64_t need = n_tokens * nq * n_splits * (D + 2);
-    if (need > Q3_DECODE_STATIC_MAX_FLOATS) {
+    if (n_tokens > 65535 || nkv > 65535 || n_splits > 65535) return Q3_ERR_TOO_LARGE;
+    if (!fits_static_scratch(n_tokens, nq, n_splits)) {
         fprintf(stderr,
-                "q3_attention_decode_bf16_static: %lld tokens x %d heads x %d splits x (%d + 2) = %lld float32 of "
+                "q3_attention_decode_bf16_static: %lld tokens x %d heads x %d splits x (%d + 2) float32 of "
                 "scratch, the built-in array holds %d; use fewer splits or tokens, or q3_attention_decode_bf16 with "
                 "a scratch buffer of your own\n",
-                (long long)n_tokens, nq, n_splits, D, (long long)need, Q3_DECODE_STATIC_MAX_FLOATS);
+                (long long)n_tokens, nq, n_splits, D, Q3_DECODE_STATIC_MAX_FLOATS);
         return Q3_ERR_STATIC_SCRATCH;
     }
     int device = -1;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return (int)e;
     if (device < 0 || device >= MAX_DEVICES) return Q3_ERR_BAD_SIZE;
-    if (!g_device_ready[device]) {
+    if (!g_device_ready[device].load(std::memory_order_acquire)) {
         const int rc = prepare_device(device);
         if (rc != 0) return rc;
     }

@@ -19,7 +19,11 @@
 // Rules of use:
 //   * The first call on a device looks up the array's device address (cudaGetSymbolAddress)
 //     and sets the kernel's shared-memory attribute.  Make that first call outside any
-//     stream capture, with the device current that the call is meant for.
+//     stream capture, with the device current that the call is meant for.  `stream` has to be
+//     a stream of the current device: the array's address is looked up for that device, and
+//     nothing here can tell which device a stream belongs to.  Host threads may make their
+//     first calls at the same time (the set-up is guarded); the rule on overlapping calls
+//     below holds for threads as it does for streams.
 //   * All calls share the one array.  Nothing in it has to be zero: every slot a call reads
 //     it has written before, so the previous call's contents do no harm.  Two calls that
 //     overlap on the GPU (different streams, or graphs replayed concurrently) race on it;

@@ -45,7 +45,6 @@ __global__ void __launch_bounds__(WARPS * 32, MINB)
 gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT* __restrict__ Y, int M, int N, int K) {
     extern __shared__ __align__(16) float red[];   // [WARPS][8*MT][16*R + 1]
     constexpr int ROWS = 16 * R, COLS = 8 * MT, LD = ROWS + 1;
-    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane >> 2, tq = lane & 3;
     const int n0 = blockIdx.x * ROWS;
     const int nkb = (K + 31) >> 5;
@@ -114,6 +113,9 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT*
             load_x(s, kb + s + PF);
         }
     }
+
+    // the stream of W is over: the next kernel may start fetching its own weights while this one adds up
+    pdl_launch_dependents();
 
     // accumulator (row n = quad [+8], column m = 2*tq [+1]) -> red[warp][m][n]
     float* mine = red + warp * COLS * LD;

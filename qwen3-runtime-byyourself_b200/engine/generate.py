@@ -59,10 +59,14 @@ def plan_batches(prompt_lengths: Sequence[int], max_new_tokens: int, n_pages: in
 
 def generate(engine, prompts: Sequence[Sequence[int]], chooser, max_new_tokens: int = 128,
              stop_token_ids: Sequence[int] = (), batch_size: Optional[int] = None,
-             on_token: Optional[Callable[[int, int], None]] = None) -> List[GenerationResult]:
+             on_token: Optional[Callable[[int, int], None]] = None,
+             sequence_ids: Optional[Sequence[int]] = None) -> List[GenerationResult]:
     """Generate for every prompt; `chooser.choose(logits, sequence_ids, steps)` picks the tokens.
 
-    `on_token(request index, token id)` is called for every new token as it is chosen."""
+    `on_token(request index, token id)` is called for every new token as it is chosen.
+    `sequence_ids[i]` names request i to the chooser (its random stream is keyed by it); by default
+    a request is named by its index, so the same prompt draws other tokens at another place of the
+    list unless it is given the same name."""
     if max_new_tokens < 0:
         raise ValueError("max_new_tokens cannot be negative")
     stops = set(int(s) for s in stop_token_ids)
@@ -76,6 +80,12 @@ def generate(engine, prompts: Sequence[Sequence[int]], chooser, max_new_tokens: 
         if len(p) + max_new_tokens > engine.max_seq_len:
             raise ValueError(f"request {i}: {len(p)} prompt tokens + {max_new_tokens} new tokens exceed the "
                              f"context of {engine.max_seq_len}")
+    if sequence_ids is None:
+        names = list(range(len(prompts)))
+    else:
+        names = [int(s) for s in sequence_ids]
+        if len(names) != len(prompts):
+            raise ValueError("sequence_ids must name every prompt")
     results = [GenerationResult() for _ in prompts]
     if max_new_tokens == 0 or not prompts:
         return results
@@ -83,7 +93,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], chooser, max_new_tokens: 
     if hasattr(chooser, "choose_async") and getattr(engine, "device_tokens", False):
         for batch in plan_batches([len(p) for p in prompts], max_new_tokens, cache.n_pages, cache.n_slots,
                                   cache.page_tokens, batch_size):
-            _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_tokens, stops, on_token)
+            _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_tokens, stops, on_token, names)
         return results
     for batch in plan_batches([len(p) for p in prompts], max_new_tokens, cache.n_pages, cache.n_slots,
                               cache.page_tokens, batch_size):
@@ -94,7 +104,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], chooser, max_new_tokens: 
             while live:
                 entries = [StepEntry(slot, feed[i], [len(feed[i]) - 1]) for i, slot in live]
                 logits = engine.step(entries)
-                chosen = chooser.choose(logits, [i for i, _ in live], [step_index] * len(live))
+                chosen = chooser.choose(logits, [names[i] for i, _ in live], [step_index] * len(live))
                 if step_index % 32 == 0 and hasattr(engine, "check_kernels"):
                     engine.check_kernels()            # now and then: a kernel whose bounded wait ran out is reported
                 still = []
@@ -126,7 +136,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], chooser, max_new_tokens: 
     return results
 
 
-def _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_tokens, stops, on_token) -> None:
+def _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_tokens, stops, on_token, names) -> None:
     """One batch with the host one step behind the device.
 
     The next step is launched before the ids of the current one have reached the host: it reads
@@ -139,7 +149,7 @@ def _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_token
     ended = set()
     try:
         logits = engine.step([StepEntry(slot, prompts[i], [len(prompts[i]) - 1]) for i, slot in live])
-        pending = chooser.choose_async(logits, [i for i, _ in live], [0] * len(live))
+        pending = chooser.choose_async(logits, [names[i] for i, _ in live], [0] * len(live))
         step_index = 0
         while live:
             onward = [(i, slot) for i, slot in live if i not in ended and len(results[i].token_ids) + 1 < max_new_tokens]
@@ -152,7 +162,7 @@ def _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_token
                 try:
                     logits = engine.step([StepEntry(slot, [0], [0]) for _, slot in onward],
                                          device_tokens=tokens_on_device)
-                    upcoming = chooser.choose_async(logits, [i for i, _ in onward], [step_index + 1] * len(onward))
+                    upcoming = chooser.choose_async(logits, [names[i] for i, _ in onward], [step_index + 1] * len(onward))
                 except CacheFull:
                     upcoming = None            # no room to run ahead: fall back to waiting for the ids first
             chosen = pending.result()
@@ -178,7 +188,7 @@ def _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_token
                 onward = [(i, slot) for i, slot in onward if i not in ended]
                 if onward:
                     logits = engine.step([StepEntry(slot, [results[i].token_ids[-1]], [0]) for i, slot in onward])
-                    upcoming = chooser.choose_async(logits, [i for i, _ in onward], [step_index] * len(onward))
+                    upcoming = chooser.choose_async(logits, [names[i] for i, _ in onward], [step_index] * len(onward))
             live, pending = (onward, upcoming) if upcoming is not None else ([], None)
         if hasattr(engine, "check_kernels"):
             engine.check_kernels()

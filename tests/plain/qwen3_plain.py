@@ -153,17 +153,22 @@ def output_weight(cfg, w):
     return w["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else w["lm_head.weight"]
 
 
-def forward(cfg, weights, token_ids, rnd=identity, rnd_logits=None):
-    """Logits [T, V] at every position of one sequence that starts at position 0:
+def forward(cfg, weights, token_ids, rnd=identity, rnd_logits=None, rows=None):
+    """Logits [T, V] at every position of one sequence that starts at position 0 (or only at
+    the positions `rows`, [len(rows), V]):
     embedding -> layers -> final norm (src/model/model.cpp:107-147) -> output
-    projection (src/model/lm_head.cpp:188-191, there for the last row only)."""
-    w = {k: np.asarray(v, dtype=np.float64) for k, v in weights.items()}
+    projection (src/model/lm_head.cpp:188-191, there for the last row only).
+    Every product widens its operands to float64 where it uses them, so large tables may be
+    handed over in a narrower type that holds their values exactly."""
+    w = weights
     T = len(token_ids)
     positions = np.arange(T)
     cos, sin = rope_table(T, cfg["head_dim"], cfg["rope_theta"])
     x = embedding(token_ids, w["model.embed_tokens.weight"])
     for layer in range(cfg["num_hidden_layers"]):
         x = decoder_layer(x, positions, cfg, w, layer, cos, sin, rnd)
+    if rows is not None:
+        x = x[np.asarray(rows, dtype=np.int64)]
     x = rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"], rnd)
     return linear(x, output_weight(cfg, w), rnd if rnd_logits is None else rnd_logits)
 

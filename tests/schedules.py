@@ -77,3 +77,62 @@ def peak_tokens(steps, page=64):
         for rid in s["end"]:
             del held[rid]
     return peak
+
+
+def chunked(requests, cuts):
+    """Each request alone, its tokens fed in several steps of more than one token: `cuts[id]` lists
+    where a new step begins (so every step after the first continues a sequence at a position
+    above 0 with several tokens at once); logits at every position."""
+    steps, rows = [], []
+    for rid, toks in requests.items():
+        edges = [0] + [c for c in cuts[rid] if 0 < c < len(toks)] + [len(toks)]
+        for lo, hi in zip(edges[:-1], edges[1:]):
+            steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": toks[lo:hi], "want": list(range(hi - lo))}],
+                          "end": [rid] if hi == len(toks) else []})
+            rows.append([(rid, p) for p in range(lo, hi)])
+    return steps, rows
+
+
+def mixed(requests, first, chunk):
+    """All requests together.  Step 0 brings the first `first[id]` tokens of each.  From then on every
+    step brings, for each request that still has tokens, either one token (ids whose `chunk[id]` is 1)
+    or up to `chunk[id]` tokens at once: steps that mix sequences going on by one token with sequences
+    that continue by several.  Logits at every position."""
+    steps, rows = [], []
+    fed = {}
+    entries, out, end = [], [], []
+    for rid, toks in requests.items():
+        n = min(first[rid], len(toks))
+        entries.append({"id": rid, "tokens": toks[:n], "want": list(range(n))})
+        out += [(rid, p) for p in range(n)]
+        fed[rid] = n
+        if n == len(toks):
+            end.append(rid)
+    steps.append({"step": 0, "entries": entries, "end": end})
+    rows.append(out)
+    live = [rid for rid in requests if fed[rid] < len(requests[rid])]
+    while live:
+        entries, out, end = [], [], []
+        for rid in live:
+            lo = fed[rid]
+            hi = min(lo + chunk[rid], len(requests[rid]))
+            entries.append({"id": rid, "tokens": requests[rid][lo:hi], "want": list(range(hi - lo))})
+            out += [(rid, p) for p in range(lo, hi)]
+            fed[rid] = hi
+            if hi == len(requests[rid]):
+                end.append(rid)
+        steps.append({"step": len(steps), "entries": entries, "end": end})
+        rows.append(out)
+        live = [rid for rid in live if fed[rid] < len(requests[rid])]
+    return steps, rows
+
+
+def shrinking(live_counts, prompt_of=lambda i: 1 + i % 5):
+    """Lengths for one batch whose number of live sequences in decode step k is live_counts[k]
+    (non-increasing): request i has a prompt of prompt_of(i) tokens and then as many further
+    tokens as there are steps with more than i live sequences.  Returns (total lengths, prompt lengths)."""
+    n = live_counts[0]
+    assert all(a >= b for a, b in zip(live_counts[:-1], live_counts[1:])) and live_counts[-1] >= 1
+    prompts = [prompt_of(i) for i in range(n)]
+    totals = [prompts[i] + sum(1 for c in live_counts if c > i) for i in range(n)]
+    return totals, prompts
