@@ -97,7 +97,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -153,7 +153,7 @@ def prefill_flops(cfg, layers, T):
     return layers * (linear + attention) + 2 * V * H          # + the one row of logits that is wanted
 
 
-def decode_run(q, engine, sampler, torch, rng, batch, longest_prompt, steps, warmup, clocks=None):
+def decode_run(q, engine, sampler, torch, rng, batch, longest_prompt, steps, warmup):
     """Prefill `batch` unequal prompts in one step, then time `steps` decode steps on the device."""
     import numpy as np
     lengths = unequal_lengths(batch, longest_prompt, rng)
@@ -178,15 +178,11 @@ def decode_run(q, engine, sampler, torch, rng, batch, longest_prompt, steps, war
     torch.cuda.synchronize()
     launches_before = engine.launches
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if clocks is not None:
-        clocks.__enter__()
     start.record()
     for i in range(steps):
         one(1 + warmup + i)
     stop.record()
     torch.cuda.synchronize()
-    if clocks is not None:
-        clocks.__exit__()
     ms = start.elapsed_time(stop) / steps
     cached = sum(engine.length(s) for s in slots) - batch * steps / 2.0      # mean over the timed steps
     launches = (engine.launches - launches_before) + steps                     # + the sampler's kernel
@@ -196,23 +192,48 @@ def decode_run(q, engine, sampler, torch, rng, batch, longest_prompt, steps, war
             "longest": max(lengths) + warmup + steps}
 
 
+E2E_SETTLE_STEPS = 40
+
+
 def e2e_run(q, engine, torch, rng, batch, longest_prompt, steps, warmup):
     """Through `generate_token_ids`: host prompts in, host token ids out; the decode steps after
-    the warm-up are timed on the host clock (each ends with the device-to-host read of its ids)."""
+    the warm-up are timed on the host clock (each ends with the device-to-host read of its ids).
+
+    The entry point runs all prompts of the batch as ONE step (tens of thousands of tokens at the power
+    limit), after which the SM clock needs some 100 ms to come back up; decode steps in that tail run at
+    the lower clock.  So the warm-up here is `warmup` + E2E_SETTLE_STEPS untimed decode steps, and the
+    number is that of generation in steady state.  `host_ms` is what the host spends per step on
+    launching (step + choice), not counting its wait for the ids."""
     lengths = unequal_lengths(batch, longest_prompt, rng)
     prompts = [rng.integers(0, engine.vocab_size, size=n).tolist() for n in lengths]
-    marks = []
+    warmup = warmup + E2E_SETTLE_STEPS
+    marks, busy = [], [0.0, 0]
 
     def on_token(index, token):
         if index == 0:
             marks.append(time.perf_counter())
 
-    q.generate_token_ids(engine, prompts, q.SamplingParams(mode="greedy"),
-                         q.GenerationOptions(max_new_tokens=1 + warmup + steps), on_token=on_token)
+    real_step = engine.step
+
+    def timed_step(*a, **k):
+        t0 = time.perf_counter()
+        out = real_step(*a, **k)
+        if len(marks) > warmup:
+            busy[0] += time.perf_counter() - t0
+            busy[1] += 1
+        return out
+
+    engine.step = timed_step
+    try:
+        q.generate_token_ids(engine, prompts, q.SamplingParams(mode="greedy"),
+                             q.GenerationOptions(max_new_tokens=1 + warmup + steps), on_token=on_token)
+    finally:
+        del engine.step
     torch.cuda.synchronize()
     # marks[k] is taken after step k's ids reached the host; step 0 is the prefill
     seconds = marks[warmup + steps] - marks[warmup]
-    return {"tok_s": batch * steps / seconds, "ms": seconds / steps * 1e3}
+    return {"tok_s": batch * steps / seconds, "ms": seconds / steps * 1e3, "warmup": warmup,
+            "host_ms": busy[0] / max(busy[1], 1) * 1e3}
 
 
 def main() -> int:
@@ -258,10 +279,11 @@ def main() -> int:
 
     # headline: batch 8 whose longest sequence ends at the context length
     clocks = ClockSampler()
-    head = decode_run(q, engine, sampler, torch, rng, batch, CONTEXT - warmup - args.steps - 1, args.steps, warmup, clocks)
+    clocks.__enter__()                    # sampled through every arm, warm-up included
+    head = decode_run(q, engine, sampler, torch, rng, batch, CONTEXT - warmup - args.steps - 1, args.steps, warmup)
     step_bytes = weight_bytes_per_step(cfg, layers, batch) + head["cached_tokens"] * engine.cache.bytes_per_token()
     achieved = step_bytes / (head["ms"] * 1e-3) / 1e9
-    e2e = e2e_run(q, engine, torch, rng, batch, CONTEXT - warmup - args.steps - 1, args.steps, warmup)
+    e2e = e2e_run(q, engine, torch, rng, batch, CONTEXT - warmup - E2E_SETTLE_STEPS - args.steps - 1, args.steps, warmup)
     h2d = engine.last_upload_bytes
 
     points = {}
@@ -286,6 +308,7 @@ def main() -> int:
             times.append(start.elapsed_time(stop))
     prefill_ms = statistics.median(times)
     flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
+    clocks.__exit__()
 
     line = {
         "metric": f"decode tok/s at batch {batch}, context {CONTEXT} (Qwen3-{args.shape.upper()} shape, random weights, 1 B200)",
@@ -300,7 +323,8 @@ def main() -> int:
                    "cache": "paged, 64 tokens a page", "l2": "a step reads every weight (GBs), far above the 126 MB L2",
                    "sampling": "greedy on the device"},
         "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms"], 4),
-                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4 * batch},
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4 * batch, "warmup": e2e["warmup"],
+                "host_ms_per_step": round(e2e["host_ms"], 4)},
         "gpu_launches": int(head["launches"]),
         "prefill": {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
                     "ms": round(prefill_ms, 3),
