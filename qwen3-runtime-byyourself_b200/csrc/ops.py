@@ -329,25 +329,6 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Te
     return out
 
 
-def gemm_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False, variant: int = 0,
-                blocks: int = 0) -> torch.Tensor:
-    """out[M, N] = x[M, K] . w[N, K]^T for M <= 16 with W streamed by TMA through per-warp rings of a
-    persistent kernel; `gated`: w holds gate and up rows interleaved in blocks of eight and out is
-    [M, N/2] = round(silu(g)) * u.  bfloat16 operands, out bfloat16 (or float32 when not gated)."""
-    M, K = x.shape
-    N = w.shape[0]
-    if w.shape[1] != K or out.shape != (M, N // 2 if gated else N) or K % 8 != 0 or M > 16 or (gated and N % 16 != 0):
-        raise KernelError(f"gemm_stream: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
-    if out.dtype not in ((torch.bfloat16,) if gated else (torch.bfloat16, torch.float32)):
-        raise KernelError("gemm_stream: output must be bfloat16 (or float32 when not gated)")
-    fn = _fn("gemm_stream.cu", "q3_gemm_stream_bf16",
-             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), M, N, K,
-              int(out.dtype == torch.float32), int(gated), int(variant), int(blocks), _status_word(x.device).data_ptr(),
-              _stream()), "gemm_stream")
-    return out
-
-
 # ------------------------------------------------------------------ bfloat16 prompt attention
 def attention_prefill(q, k_pages, v_pages, out, seq_start, seq_pos0, page_table, n_seqs: int, max_new: int, nq: int,
                       nkv: int, d: int, scale: float, window: Optional[int] = None):
