@@ -13,6 +13,13 @@
 // the rows of one m16n8k16 tile, so the group's K and V are read once.  The warps' partial
 // results are merged in shared memory, the splits' in a second small kernel through a
 // float32 scratch buffer.  Compiled for one head size: -DQ3_HEAD_DIM=<multiple of 16>.
+//
+// The fused form does the whole attention of a decode step in one launch: it takes the output of
+// the q/k/v projection as it is, normalises and rotates the group's query heads itself (what
+// qkv_prepare does, src/model/self_attention.cpp:147-152), the block that owns the sequence's last
+// page does the same for the new key, writes key and value into the cache and puts them into its own
+// copy of the page, and the splits of a (sequence, kv head) form a thread-block cluster that merges
+// its partial results through distributed shared memory: no scratch buffer, no second and third kernel.
 #include "common.cuh"
 
 #ifndef Q3_HEAD_DIM
@@ -36,6 +43,12 @@ static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size: multiples of 16 up
 constexpr int SMEM_PIPE = WARPS * STAGES * 2 * PANEL_BYTES;
 constexpr int SMEM_MERGE = WARPS * 16 * (D + 2) * 4;
 constexpr int SMEM_BYTES = SMEM_PIPE > SMEM_MERGE ? SMEM_PIPE : SMEM_MERGE;
+// the fused form keeps, behind the pipeline: first the prepared queries [16][D] and the new key and value
+// (bf16), later - in the same place - the block's merged result [16][D] float32 and its (max, sum) pairs
+constexpr int SMEM_PREP = (16 + 2) * D * 2;
+constexpr int SMEM_RESULT = 16 * (D + 2) * 4;
+constexpr int SMEM_FUSED = SMEM_BYTES + (SMEM_PREP > SMEM_RESULT ? SMEM_PREP : SMEM_RESULT);
+constexpr int MAX_CLUSTER = 8;                     // the portable cluster size: the fused form takes up to 8 splits
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -63,6 +76,83 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) {
+    uint32_t addr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+// One head vector of the projection output, normalised (if `norm_w`) and rotated (if `cos_tab`), by one warp:
+// lane owns the pairs (i, i + D/2), i = lane + 32 n, exactly as qkv_prepare does (attention.cu), so the values
+// are the same to the bit.  dst: D bf16.
+__device__ __forceinline__ void prepare_head(const bf16* __restrict__ src, bf16* dst, const float* __restrict__ norm_w,
+                                             const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int pos,
+                                             float eps, int lane) {
+    constexpr int HALF = D / 2, ITER = (HALF + 31) / 32;
+    float a[ITER], b[ITER], wa[ITER], wb[ITER], cs[ITER], sn[ITER];
+    // every load first (they do not depend on one another), then the arithmetic
+#pragma unroll
+    for (int n = 0; n < ITER; ++n) {
+        const int i = lane + 32 * n;
+        a[n] = b[n] = 0.0f;
+        wa[n] = wb[n] = cs[n] = 1.0f;
+        sn[n] = 0.0f;
+        if (i < HALF) {
+            a[n] = __bfloat162float(src[i]);
+            b[n] = __bfloat162float(src[i + HALF]);
+            if (norm_w != nullptr) {
+                wa[n] = norm_w[i];
+                wb[n] = norm_w[i + HALF];
+            }
+            if (cos_tab != nullptr) {
+                cs[n] = cos_tab[(int64_t)pos * HALF + i];
+                sn[n] = sin_tab[(int64_t)pos * HALF + i];
+            }
+        }
+    }
+    float sq = 0.0f;
+#pragma unroll
+    for (int n = 0; n < ITER; ++n) sq += a[n] * a[n] + b[n] * b[n];      // lanes beyond the head add zeros
+    if (norm_w != nullptr) {
+        const float inv = rsqrtf(warp_sum(sq) / (float)D + eps);
+#pragma unroll
+        for (int n = 0; n < ITER; ++n) {
+            a[n] = round_to<bf16>(round_to<bf16>(a[n] * inv) * wa[n]);
+            b[n] = round_to<bf16>(round_to<bf16>(b[n] * inv) * wb[n]);
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < ITER; ++n) {
+        const int i = lane + 32 * n;
+        if (i < HALF) {
+            float x = a[n], y = b[n];
+            if (cos_tab != nullptr) {
+                x = a[n] * cs[n] - b[n] * sn[n];
+                y = b[n] * cs[n] + a[n] * sn[n];
+            }
+            dst[i] = __float2bfloat16_rn(x);
+            dst[i + HALF] = __float2bfloat16_rn(y);
+        }
+    }
+}
+
+// What the fused form needs beyond the split form's arguments.
+struct FusedArgs {
+    const bf16* qkv;               // [tokens, (nq + 2 nkv) * D]: the projection output as it is
+    bf16* out;                     // [tokens, nq * D]
+    const float* q_norm_w;         // [D] or null
+    const float* k_norm_w;
+    const float* cos_tab;          // [positions, D/2] or null
+    const float* sin_tab;
+    float eps;
+    int write_kv;                  // 0: the layer reads another layer's cache, which holds the new key and value already
+};
+
 // Copies one warp's panel (16 keys x D) of a page into padded shared rows.
 __device__ __forceinline__ void load_panel(uint32_t dst, const bf16* src, int lane) {
 #pragma unroll
@@ -73,11 +163,13 @@ __device__ __forceinline__ void load_panel(uint32_t dst, const bf16* src, int la
 }
 
 // part_o: [tokens, nq, splits, D] float32 (unnormalised sums); part_ml: [tokens, nq, splits, 2] (max, sum).
+// FUSED: `q`, `part_o` and `part_ml` are unused; the grid's x dimension is a cluster.
+template <bool FUSED>
 __global__ void __launch_bounds__(WARPS * 32)
-decode_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+decode_split_kernel(const bf16* __restrict__ q, const bf16* k_pages, const bf16* v_pages,
                     float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ token_seq,
                     const int* __restrict__ token_pos, const int* __restrict__ page_table, int pages_per_seq, int nq,
-                    int nkv, float scale_log2, int window) {
+                    int nkv, float scale_log2, int window, const FusedArgs fused) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_wait();
     const int split = blockIdx.x, n_splits = gridDim.x, kvh = blockIdx.y, t = blockIdx.z;
@@ -93,10 +185,48 @@ decode_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     const int pg_end = min(first_page + n_pages, pg_begin + per_split);
     const int count = max(pg_end - pg_begin, 0);
 
+    // the first pages are asked for before anything else: what follows runs under their flight
+    const uint32_t pipe = smem_u32(smem) + warp * (STAGES * 2 * PANEL_BYTES);
+    auto issue = [&](int i) {
+        if (i < count) {
+            const int64_t base = (((int64_t)pages[pg_begin + i] * nkv + kvh) * PAGE + warp * KEYS_PER_WARP) * D;
+            const uint32_t dst = pipe + (i % STAGES) * (2 * PANEL_BYTES);
+            load_panel(dst, k_pages + base, lane);
+            load_panel(dst + PANEL_BYTES, v_pages + base, lane);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) issue(s);
+
+    // the block that holds the sequence's last page owns the new token's key and value
+    const bool owner = FUSED && fused.write_kv && count > 0 && pg_end == first_page + n_pages;
+    bf16* prep = reinterpret_cast<bf16*>(smem + SMEM_BYTES);            // [16][D] queries, then the new key, then the new value
+    if constexpr (FUSED) {
+        const bf16* row = fused.qkv + (int64_t)t * (nq + 2 * nkv) * D;
+        for (int r = warp; r < G; r += WARPS)
+            prepare_head(row + (int64_t)(kvh * G + r) * D, prep + r * D, fused.q_norm_w, fused.cos_tab, fused.sin_tab, pos,
+                         fused.eps, lane);
+        if (owner) {
+            if (warp == (G % WARPS))
+                prepare_head(row + (int64_t)(nq + kvh) * D, prep + 16 * D, fused.k_norm_w, fused.cos_tab, fused.sin_tab, pos,
+                             fused.eps, lane);
+            if (warp == ((G + 1) % WARPS))
+                for (int i = lane; i < D; i += 32) prep[17 * D + i] = row[(int64_t)(nq + nkv + kvh) * D + i];
+        }
+        __syncthreads();
+        if (owner) {       // into the cache for the steps to come; this step reads them from `prep`
+            const int64_t at = (((int64_t)pages[pos / PAGE] * nkv + kvh) * PAGE + pos % PAGE) * D;
+            for (int i = threadIdx.x; i < D; i += WARPS * 32) {
+                const_cast<bf16*>(k_pages)[at + i] = prep[16 * D + i];
+                const_cast<bf16*>(v_pages)[at + i] = prep[17 * D + i];
+            }
+        }
+    }
     // query rows of the group as A fragments: row r = head kvh*G + r (rows >= G are zero)
     uint32_t qa[KT][4];
     {
-        const bf16* q0 = q + ((int64_t)t * nq + (int64_t)kvh * G) * D;
+        const bf16* q0 = FUSED ? prep : q + ((int64_t)t * nq + (int64_t)kvh * G) * D;
 #pragma unroll
         for (int kt = 0; kt < KT; ++kt) {
             const int c = kt * 16 + tq * 2;
@@ -112,24 +242,24 @@ decode_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};   // rows quad and quad + 8
 
-    const uint32_t pipe = smem_u32(smem) + warp * (STAGES * 2 * PANEL_BYTES);
-    auto issue = [&](int i) {
-        if (i < count) {
-            const int64_t base = (((int64_t)pages[pg_begin + i] * nkv + kvh) * PAGE + warp * KEYS_PER_WARP) * D;
-            const uint32_t dst = pipe + (i % STAGES) * (2 * PANEL_BYTES);
-            load_panel(dst, k_pages + base, lane);
-            load_panel(dst + PANEL_BYTES, v_pages + base, lane);
-        }
-        cp_async_commit();
-    };
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) issue(s);
-
     for (int i = 0; i < count; ++i) {
         cp_async_wait<STAGES - 2>();
         __syncwarp();
         issue(i + STAGES - 1);      // its stage was consumed in iteration i - 1
         const uint32_t kbuf = pipe + (i % STAGES) * (2 * PANEL_BYTES), vbuf = kbuf + PANEL_BYTES;
+        if constexpr (FUSED) {
+            // the new token's own key and value: not in the cache when this page was asked for
+            if (owner && i == count - 1 && (pos % PAGE) / KEYS_PER_WARP == warp) {
+                unsigned char* stage = smem + warp * (STAGES * 2 * PANEL_BYTES) + (i % STAGES) * (2 * PANEL_BYTES);
+                const int key_row = (pos % PAGE) % KEYS_PER_WARP;
+                for (int c = lane; c < D / 8; c += 32) {
+                    *reinterpret_cast<uint4*>(stage + key_row * ROW_BYTES + c * 16) = *reinterpret_cast<const uint4*>(prep + 16 * D + c * 8);
+                    *reinterpret_cast<uint4*>(stage + PANEL_BYTES + key_row * ROW_BYTES + c * 16) =
+                        *reinterpret_cast<const uint4*>(prep + 17 * D + c * 8);
+                }
+                __syncwarp();
+            }
+        }
 
         // scores of the group's rows against this warp's 16 keys
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -221,6 +351,8 @@ decode_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         }
     }
     __syncthreads();
+    float* res_o = reinterpret_cast<float*>(smem + SMEM_BYTES);         // FUSED: [16][D], then (max, sum) [16][2]
+    float* res_ml = res_o + 16 * D;
     for (int idx = threadIdx.x; idx < G * D; idx += WARPS * 32) {
         const int row = idx / D, c = idx % D;
         float m = -INFINITY;
@@ -234,12 +366,51 @@ decode_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
             acc += f * sm_o[(w * 16 + row) * D + c];
             l += f * sm_ml[(w * 16 + row) * 2 + 1];
         }
-        const int64_t slot = ((int64_t)t * nq + kvh * G + row) * n_splits + split;
-        part_o[slot * D + c] = acc;
-        if (c == 0) {
-            part_ml[slot * 2 + 0] = m;
-            part_ml[slot * 2 + 1] = l;
+        if constexpr (FUSED) {
+            res_o[row * D + c] = acc;
+            if (c == 0) {
+                res_ml[row * 2 + 0] = m;
+                res_ml[row * 2 + 1] = l;
+            }
+        } else {
+            const int64_t slot = ((int64_t)t * nq + kvh * G + row) * n_splits + split;
+            part_o[slot * D + c] = acc;
+            if (c == 0) {
+                part_ml[slot * 2 + 0] = m;
+                part_ml[slot * 2 + 1] = l;
+            }
         }
+    }
+    if constexpr (FUSED) {
+        // the splits of this (sequence, kv head) are the blocks of one cluster: each finishes a share of the
+        // group's values from everybody's partial results, in split order (the order of the merge kernel)
+        cluster_sync_all();
+        for (int idx = threadIdx.x * n_splits + split; idx < G * D; idx += WARPS * 32 * n_splits) {
+            const int row = idx / D, c = idx % D;
+            float ms[MAX_CLUSTER], ls[MAX_CLUSTER], os[MAX_CLUSTER];
+#pragma unroll
+            for (int s2 = 0; s2 < MAX_CLUSTER; ++s2) {               // every peer's values first, then the arithmetic
+                ms[s2] = -INFINITY;
+                ls[s2] = os[s2] = 0.0f;
+                if (s2 < n_splits) {
+                    ms[s2] = ld_peer_f32(res_ml + row * 2, s2);
+                    ls[s2] = ld_peer_f32(res_ml + row * 2 + 1, s2);
+                    os[s2] = ld_peer_f32(res_o + row * D + c, s2);
+                }
+            }
+            float m = -INFINITY;
+#pragma unroll
+            for (int s2 = 0; s2 < MAX_CLUSTER; ++s2) m = fmaxf(m, ms[s2]);
+            float l = 0.0f, acc = 0.0f;
+#pragma unroll
+            for (int s2 = 0; s2 < MAX_CLUSTER; ++s2)
+                if (s2 < n_splits) l += ms[s2] == -INFINITY ? 0.0f : exp2f(ms[s2] - m) * ls[s2];
+#pragma unroll
+            for (int s2 = 0; s2 < MAX_CLUSTER; ++s2)
+                if (s2 < n_splits) acc += (ms[s2] == -INFINITY ? 0.0f : exp2f(ms[s2] - m)) * os[s2];
+            fused.out[((int64_t)t * nq + kvh * G + row) * D + c] = __float2bfloat16_rn(acc / l);
+        }
+        cluster_sync_all();      // nobody leaves while its results are still being read
     }
 }
 
@@ -283,17 +454,56 @@ Q3_EXPORT int q3_attention_decode_bf16(const void* q, const void* k_pages, const
     cudaStream_t stream = (cudaStream_t)stream_;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     float* part_o = scratch;
     float* part_ml = scratch + n_tokens * nq * n_splits * D;
     const dim3 grid(n_splits, nkv, (unsigned)n_tokens);
-    cudaError_t e = q3_launch(decode_split_kernel, grid, dim3(WARPS * 32), SMEM_BYTES, stream, (const bf16*)q,
+    cudaError_t e = q3_launch(decode_split_kernel<false>, grid, dim3(WARPS * 32), SMEM_BYTES, stream, (const bf16*)q,
                               (const bf16*)k_pages, (const bf16*)v_pages, part_o, part_ml, token_seq, token_pos, page_table,
-                              pages_per_seq, nq, nkv, scale * 1.4426950408889634f, window);
+                              pages_per_seq, nq, nkv, scale * 1.4426950408889634f, window, FusedArgs{});
     if (e != cudaSuccess) return (int)e;
     return (int)q3_launch(decode_merge_kernel, dim3(nq, (unsigned)n_tokens), dim3(D < 128 ? 32 : 128), 0, stream,
                           (const float*)part_o, (const float*)part_ml, (bf16*)out, nq, n_splits);
+}
+
+// The whole attention of a decode step in one launch (see the top of the file): `qkv` is the projection output
+// [tokens, (nq + 2 nkv) * head size]; norm weights and rotation tables may be null; `n_splits` <= 8.
+Q3_EXPORT int q3_attention_decode_fused_bf16(const void* qkv, void* k_pages, void* v_pages, void* out, const float* q_norm_w,
+                                             const float* k_norm_w, const float* cos_tab, const float* sin_tab, float eps,
+                                             const int* token_seq, const int* token_pos, const int* page_table,
+                                             int pages_per_seq, int64_t n_tokens, int nq, int nkv, float scale, int window,
+                                             int n_splits, int write_kv, void* stream_) {
+    if (n_tokens <= 0) return 0;
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || n_splits <= 0 || n_splits > MAX_CLUSTER) return Q3_ERR_BAD_SIZE;
+    if ((cos_tab == nullptr) != (sin_tab == nullptr)) return Q3_ERR_BAD_SIZE;
+    if (n_tokens > 65535 || nkv > 65535) return Q3_ERR_TOO_LARGE;
+    if (!aligned16(qkv) || !aligned16(k_pages) || !aligned16(v_pages)) return Q3_ERR_MISALIGNED;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    static bool configured[64] = {false};
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= 64) return Q3_ERR_BAD_SIZE;
+    if (!configured[device]) {
+        e = cudaFuncSetAttribute(decode_split_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_FUSED);
+        if (e != cudaSuccess) return (int)e;
+        configured[device] = true;
+    }
+    FusedArgs fused;
+    fused.qkv = (const bf16*)qkv;
+    fused.out = (bf16*)out;
+    fused.q_norm_w = q_norm_w;
+    fused.k_norm_w = k_norm_w;
+    fused.cos_tab = cos_tab;
+    fused.sin_tab = sin_tab;
+    fused.eps = eps;
+    fused.write_kv = write_kv;
+    const dim3 grid(n_splits, nkv, (unsigned)n_tokens);
+    return (int)q3_launch_cluster(decode_split_kernel<true>, grid, dim3(WARPS * 32), (size_t)SMEM_FUSED, stream, dim3(n_splits, 1, 1),
+                                  (const bf16*)nullptr, (const bf16*)k_pages, (const bf16*)v_pages, (float*)nullptr, (float*)nullptr,
+                                  token_seq, token_pos, page_table, pages_per_seq, nq, nkv, scale * 1.4426950408889634f, window,
+                                  fused);
 }

@@ -30,7 +30,7 @@ int prepare_device(int device) {
     float* address = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&address, g_static_scratch);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    e = cudaFuncSetAttribute(decode_split_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     g_scratch_address[device] = address;
     g_device_ready[device].store(true, std::memory_order_release);
@@ -76,9 +76,9 @@ Q3_EXPORT int q3_attention_decode_bf16_static(const void* q, const void* k_pages
     float* part_o = g_scratch_address[device];
     float* part_ml = part_o + n_tokens * nq * n_splits * D;
     const dim3 grid(n_splits, nkv, (unsigned)n_tokens);
-    e = q3_launch(decode_split_kernel, grid, dim3(WARPS * 32), SMEM_BYTES, stream, (const bf16*)q, (const bf16*)k_pages,
+    e = q3_launch(decode_split_kernel<false>, grid, dim3(WARPS * 32), SMEM_BYTES, stream, (const bf16*)q, (const bf16*)k_pages,
                   (const bf16*)v_pages, part_o, part_ml, token_seq, token_pos, page_table, pages_per_seq, nq, nkv,
-                  scale * 1.4426950408889634f, window);
+                  scale * 1.4426950408889634f, window, FusedArgs{});
     if (e != cudaSuccess) return (int)e;
     return (int)q3_launch(decode_merge_kernel, dim3(nq, (unsigned)n_tokens), dim3(D < 128 ? 32 : 128), 0, stream,
                           (const float*)part_o, (const float*)part_ml, (bf16*)out, nq, n_splits);

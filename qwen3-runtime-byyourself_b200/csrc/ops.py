@@ -152,6 +152,8 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
         raise KernelError("rms_norm: weight or output does not fit")
     if delta is not None and (delta.shape != x.shape or delta.dtype != x.dtype):
         raise KernelError("rms_norm: delta does not fit")
+    if out.data_ptr() == x.data_ptr():
+        raise KernelError("rms_norm: the output may not be the input's own memory")
     fn = _fn("elementwise.cu", f"q3_rms_norm_{s}",
              [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_int64, c_int64, c_void_p])
     _check(fn(_dev(x, "x"), _ptr(delta, "delta"), _dev(weight, "weight", torch.float32), _dev(out, "out"),
@@ -277,7 +279,7 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float, top_k: i
 
 
 # ------------------------------------------------------------------ bfloat16 decode attention
-def attention_decode_splits(n_tokens: int, nkv: int, sm_count: int = 148) -> int:
+def attention_decode_splits(n_tokens: int, nkv: int, sm_count: int) -> int:
     """Key splits such that the whole grid (splits x kv heads x tokens) is resident at once, two
     blocks per SM, and at most 16: fixed by the batch size alone.  (Measured at batch 8, 4,096
     keys: 4 splits 29 us, 5 splits - a second wave - 39 us.)"""
@@ -303,6 +305,33 @@ def attention_decode(q, k_pages, v_pages, out, scratch, token_seq, token_pos, pa
               _dev(page_table, "page_table", torch.int32), page_table.shape[-1], n_tokens, nq, nkv, float(scale),
               int(window or 0), int(n_splits), _stream()), "attention_decode")
     _count_extra(1)
+    return out
+
+
+FUSED_DECODE_MAX_SPLITS = 8
+
+
+def attention_decode_fused(qkv, k_pages, v_pages, out, q_norm_w, k_norm_w, cos, sin, eps: float, token_seq, token_pos,
+                           page_table, n_tokens: int, nq: int, nkv: int, d: int, scale: float, window: Optional[int],
+                           n_splits: int, write_kv: bool = True):
+    """The attention of a decode step in one launch: per-head norm and rotation of the new query and key, the
+    write of key and value into the cache pages, attention over the pages split over the keys, and the merge of
+    the splits inside a thread-block cluster.  `qkv` is the projection output [tokens, (nq + 2 nkv) * d]."""
+    if qkv.dtype != torch.bfloat16:
+        raise KernelError("attention_decode_fused is a bfloat16 kernel")
+    if nq // nkv > 16 or d % 16 != 0 or d > 256 or not 0 < n_splits <= FUSED_DECODE_MAX_SPLITS:
+        raise KernelError(f"attention_decode_fused: group of {nq // nkv} heads, head_dim {d} or {n_splits} splits not supported")
+    if qkv.shape[-1] != (nq + 2 * nkv) * d or k_pages.shape[1:] != (nkv, 64, d) or out.shape[-1] != nq * d:
+        raise KernelError("attention_decode_fused: shapes do not fit")
+    fn = _fn("attention_decode.cu", "q3_attention_decode_fused_bf16",
+             [c_void_p] * 8 + [c_float] + [c_void_p] * 3 + [c_int, c_int64, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
+             defines=(f"Q3_HEAD_DIM={d}",))
+    _check(fn(_dev(qkv, "qkv"), _dev(k_pages, "k_pages", torch.bfloat16), _dev(v_pages, "v_pages", torch.bfloat16),
+              _dev(out, "out", torch.bfloat16), _ptr(q_norm_w, "q_norm_w", torch.float32), _ptr(k_norm_w, "k_norm_w", torch.float32),
+              _ptr(cos, "cos", torch.float32), _ptr(sin, "sin", torch.float32), float(eps),
+              _dev(token_seq, "token_seq", torch.int32), _dev(token_pos, "token_pos", torch.int32),
+              _dev(page_table, "page_table", torch.int32), page_table.shape[-1], n_tokens, nq, nkv, float(scale),
+              int(window or 0), int(n_splits), int(bool(write_kv)), _stream()), "attention_decode_fused")
     return out
 
 

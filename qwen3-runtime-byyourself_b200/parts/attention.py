@@ -24,6 +24,9 @@ from .linear import linear
 # Hand-written bfloat16 kernels register themselves here: fn(part, q, cache, out, ctx, table) -> bool
 PREFILL_KERNELS = []
 DECODE_KERNELS = []
+# Kernels that take the projection output as it is and do norm, rotation, cache write and attention of a decode
+# step in one launch: fn(part, qkv, cache, out, ctx, table, q_norm_w, k_norm_w, eps, cos, sin) -> bool
+FUSED_DECODE_KERNELS = []
 
 
 class GQAAttention(Part):
@@ -72,22 +75,27 @@ class GQAAttention(Part):
         table = ctx.page_tables[cache.group]
         qkv = ctx.scratch.get("attn.qkv", (N, (nq + 2 * nkv) * d), ctx.dtype)
         linear(x, self.w_qkv, qkv)
-        q = ctx.scratch.get("attn.q", (N, nq * d), ctx.dtype)
+        attn = ctx.scratch.get("attn.ctx", (N, nq * d), ctx.dtype)
+        out = ctx.scratch.get("mixer.out", (N, self.hidden_size), ctx.dtype)
         norm_eps = self.q_norm.eps if self.q_norm is not None else 0.0
         qw = self.q_norm.weight if self.q_norm is not None else None
         kw = self.k_norm.weight if self.k_norm is not None else None
-        if self.position is None or getattr(self.position, "fused_tables", False):
-            cos = sin = None
-            if self.position is not None:
-                self.position.prepare(ctx.max_positions, ctx.device)
-                cos, sin = self.position.cos, self.position.sin
+        tables = self.position is None or getattr(self.position, "fused_tables", False)
+        cos = sin = None
+        if tables and self.position is not None:
+            self.position.prepare(ctx.max_positions, ctx.device)
+            cos, sin = self.position.cos, self.position.sin
+        if tables and ctx.is_decode and ctx.dtype == torch.bfloat16:
+            for kernel in FUSED_DECODE_KERNELS:
+                if kernel(self, qkv, cache, attn, ctx, table, qw, kw, norm_eps, cos, sin):
+                    return linear(attn, self.w_o, out)
+        q = ctx.scratch.get("attn.q", (N, nq * d), ctx.dtype)
+        if tables:
             ops.qkv_prepare(qkv, q, cache.keys, cache.values, qw, kw, cos, sin, ctx.token_seq, ctx.token_pos, table,
                             N, nq, nkv, d, norm_eps, write_kv=not cache.shared)
         else:
             self._prepare_unfused(qkv, q, cache, ctx, table, qw, kw, norm_eps)
-        attn = ctx.scratch.get("attn.ctx", (N, nq * d), ctx.dtype)
         self.attend(q, cache, attn, ctx, table)
-        out = ctx.scratch.get("mixer.out", (N, self.hidden_size), ctx.dtype)
         return linear(attn, self.w_o, out)
 
     def attend(self, q, cache, out, ctx, table) -> None:
@@ -104,9 +112,11 @@ class GQAAttention(Part):
         N = ctx.n_tokens
         qs = qkv[:, :nq * d].contiguous().view(N, nq, d)
         ks = qkv[:, nq * d:(nq + nkv) * d].contiguous().view(N, nkv, d)
-        if qw is not None:
-            ops.rms_norm(qs, qw, eps, qs)
-            ops.rms_norm(ks, kw, eps, ks)
+        if qw is not None:                                  # into buffers of their own: the norm kernel's input and
+            qn, kn = torch.empty_like(qs), torch.empty_like(ks)   # output may not be the same memory
+            ops.rms_norm(qs, qw, eps, qn)
+            ops.rms_norm(ks, kw, eps, kn)
+            qs, ks = qn, kn
         self.position.prepare(ctx.max_positions, ctx.device)
         self.position.apply_(qs, ks, ctx.token_pos[:N])
         packed = torch.cat([qs.view(N, -1), ks.view(N, -1), qkv[:, (nq + nkv) * d:]], dim=1).contiguous()
@@ -119,11 +129,35 @@ def _decode_split_kernel(part, q, cache, out, ctx, table) -> bool:
     nq, nkv, d = part.num_heads, part.num_kv_heads, part.head_dim
     if nq // nkv > 16:
         return False
-    splits = ops.attention_decode_splits(ctx.n_tokens, nkv)
+    splits = ops.attention_decode_splits(ctx.n_tokens, nkv, _sm_count(ctx.device))
     scratch = ctx.scratch.get("attn.decode_scratch", (ctx.n_tokens * nq * splits * (d + 2),), torch.float32)
     ops.attention_decode(q, cache.keys, cache.values, out, scratch, ctx.token_seq, ctx.token_pos, table, ctx.n_tokens,
                          nq, nkv, d, part.scale, part.window, splits)
     return True
+
+
+def _decode_fused_kernel(part, qkv, cache, out, ctx, table, q_norm_w, k_norm_w, eps, cos, sin) -> bool:
+    """Norm, rotation, cache write, split-key attention and the merge of the splits (inside a thread-block
+    cluster) in one launch: bfloat16, groups of up to 16 query heads, up to 8 splits."""
+    nq, nkv, d = part.num_heads, part.num_kv_heads, part.head_dim
+    if nq // nkv > 16:
+        return False
+    splits = min(ops.attention_decode_splits(ctx.n_tokens, nkv, _sm_count(ctx.device)), ops.FUSED_DECODE_MAX_SPLITS)
+    ops.attention_decode_fused(qkv, cache.keys, cache.values, out, q_norm_w, k_norm_w, cos, sin, eps, ctx.token_seq,
+                               ctx.token_pos, table, ctx.n_tokens, nq, nkv, d, part.scale, part.window, splits,
+                               write_kv=not cache.shared)
+    return True
+
+
+_sm_counts = {}
+
+
+def _sm_count(device) -> int:
+    device = torch.device(device)
+    count = _sm_counts.get(device)
+    if count is None:
+        count = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return count
 
 
 def _prefill_flash_kernel(part, q, cache, out, ctx, table) -> bool:
@@ -147,6 +181,7 @@ def _prefill_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
 tc_prefill_rows = 128     # from this many new tokens of the longest sequence on, the tcgen05 kernel runs
 
 DECODE_KERNELS.append(_decode_split_kernel)
+FUSED_DECODE_KERNELS.append(_decode_fused_kernel)
 PREFILL_KERNELS.append(_prefill_tcgen05_kernel)
 PREFILL_KERNELS.append(_prefill_flash_kernel)
 

@@ -392,6 +392,78 @@ def test_decode_attention_split_kernel(nq, nkv, d):
     assert np.max(np.abs(back(out3)[6] - want[6])) > 1e-3      # the window really hides the older keys
 
 
+@pytest.mark.parametrize("nq,nkv,d", [(4, 2, 16), (8, 1, 32), (6, 3, 48), (32, 8, 128), (16, 1, 64), (2, 2, 256), (5, 5, 80)])
+def test_decode_attention_fused_kernel(nq, nkv, d):
+    """The whole attention of a decode step in one launch, from the raw projection output: equal to the plain
+    per-head norm, rotation and attention in float64 with the reference's rounding points, for several split
+    counts; the new key and value land in the cache, at the right place of the right page and nowhere else;
+    a far key is scaled so that it stands out among hundreds, and the query norm doubles half of every head."""
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(3 * nq + d)
+    lengths = [1, 63, 64, 65, 130, 700, 1000]
+    eps, theta = 1e-5, 50000.0
+    table, kp, vp = paged_case(rng, lengths, nkv, d, "bfloat16")
+    table_d = torch.as_tensor(table).cuda()
+    keys = [rng.normal(0, 1, (n, nkv, d)) for n in lengths]       # the last row of each is overwritten by the step
+    vals = [rng.normal(0, 1, (n, nkv, d)) for n in lengths]
+    keys[5][17] *= 4.0                                            # a far key of sequence 5 ...
+    for s, n in enumerate(lengths):
+        pages = table[s, :-(-n // 64)]
+        kpad = np.zeros((len(pages) * 64, nkv, d)); kpad[:n - 1] = keys[s][:n - 1]
+        vpad = np.zeros((len(pages) * 64, nkv, d)); vpad[:n - 1] = vals[s][:n - 1]
+        kp[torch.as_tensor(pages).long().cuda()] = dev(kpad.reshape(len(pages), 64, nkv, d).transpose(0, 2, 1, 3), "bfloat16")
+        vp[torch.as_tensor(pages).long().cuda()] = dev(vpad.reshape(len(pages), 64, nkv, d).transpose(0, 2, 1, 3), "bfloat16")
+    B = len(lengths)
+    qkv = rng.normal(0, 1, (B, (nq + 2 * nkv) * d))
+    qkv_d = dev(qkv, "bfloat16")
+    qw, kw = 1.0 + 0.1 * rng.normal(size=d), 1.0 + 0.1 * rng.normal(size=d)
+    qw[: d // 2] *= 2.0                                           # ... and a query norm that doubles half of every head
+    cos, sin = plain.rope_table(max(lengths), d, theta)
+    seq = torch.arange(B, dtype=torch.int32, device="cuda")
+    pos = torch.as_tensor([n - 1 for n in lengths], dtype=torch.int32).cuda()
+    rnd = plain.round_bf16
+    raw = back(qkv_d)
+    want = np.zeros((B, nq * d))
+    new_k, new_v = [], []
+    for s, n in enumerate(lengths):
+        q = plain.rms_norm(raw[s, :nq * d].reshape(1, nq, d), qw.astype(np.float32).astype(np.float64), eps, rnd)
+        k = plain.rms_norm(raw[s, nq * d:(nq + nkv) * d].reshape(1, nkv, d), kw.astype(np.float32).astype(np.float64), eps, rnd)
+        q = plain.apply_rope(q, np.array([n - 1]), cos, sin, rnd)
+        k = plain.apply_rope(k, np.array([n - 1]), cos, sin, rnd)
+        v = raw[s, (nq + nkv) * d:].reshape(1, nkv, d)
+        new_k.append(k[0]); new_v.append(v[0])
+        ks, vs = stored(keys[s], "bfloat16"), stored(vals[s], "bfloat16")
+        ks[n - 1], vs[n - 1] = k[0], v[0]
+        qs = np.zeros((n, nq, d)); qs[n - 1] = q[0]
+        want[s] = plain.gqa_attention(qs, ks, vs)[n - 1].reshape(-1)
+    before_k, before_v = kp.clone(), vp.clone()
+    args = (dev(qw, "float32"), dev(kw, "float32"), dev(cos, "float32"), dev(sin, "float32"), eps, seq, pos, table_d, B, nq, nkv, d,
+            d ** -0.5, None)
+    for splits in (1, 2, 5, 8):
+        kp.copy_(before_k); vp.copy_(before_v)
+        out = torch.zeros(B, nq * d, dtype=torch.bfloat16, device="cuda")
+        ops.attention_decode_fused(qkv_d, kp, vp, out, *args, splits)
+        err = np.max(np.abs(back(out) - want))
+        assert err <= 2.5e-2, f"splits {splits}: max abs err {err:.3e}"      # the tolerance of the decode kernel, plus the rounding of q
+    # the cache: only the new token's row of every (sequence, kv head) changed, to the plain values
+    changed_k, changed_v = (kp != before_k).any(dim=-1), (vp != before_v).any(dim=-1)      # [page, kv head, slot]
+    expect = torch.zeros_like(changed_k)
+    for s, n in enumerate(lengths):
+        page, slot = int(table[s, (n - 1) // 64]), (n - 1) % 64
+        expect[page, :, slot] = True
+        assert np.max(np.abs(back(kp[page, :, slot]) - new_k[s])) <= 1e-6 + 2.0 ** -7 * np.max(np.abs(new_k[s])), s
+        assert np.array_equal(back(vp[page, :, slot]), new_v[s]), s
+    assert torch.equal(changed_k | changed_v, expect)
+    # a layer that reads another layer's cache writes nothing and finds the new key and value there
+    out2 = torch.zeros_like(out)
+    snapshot_k, snapshot_v = kp.clone(), vp.clone()
+    ops.attention_decode_fused(qkv_d, kp, vp, out2, *args, 3, write_kv=False)
+    assert torch.equal(kp, snapshot_k) and torch.equal(vp, snapshot_v)
+    assert np.max(np.abs(back(out2) - want)) <= 2.5e-2
+    with pytest.raises(ops.KernelError):
+        ops.attention_decode_fused(qkv_d, kp, vp, out2, *args, 9)
+
+
 @pytest.mark.parametrize("nq,nkv,d", [(4, 2, 16), (8, 1, 32), (6, 3, 48), (8, 2, 128), (2, 2, 256), (5, 5, 80)])
 @pytest.mark.parametrize("window", [None, 90])
 def test_prefill_attention_tiled_kernel(nq, nkv, d, window):

@@ -198,7 +198,7 @@ def test_8b_widths_in_unequal_batches(wide, dtype, monkeypatch):
     from qwen3_b200.engine.engine import Engine
     config, host, requests, wanted, exact, emulated = wide
     calls = {"pair": 0, "pair_gated": 0, "attention_tc": 0, "skinny": 0, "decode_attention": 0}
-    real_pair, real_tc, real_skinny, real_dec = ops.gemm_tcgen05_pair, ops.attention_prefill_tc, ops.gemm_skinny, ops.attention_decode
+    real_pair, real_tc, real_skinny, real_dec = ops.gemm_tcgen05_pair, ops.attention_prefill_tc, ops.gemm_skinny, ops.attention_decode_fused
 
     def pair(x, w, out, gated=False):
         calls["pair_gated" if gated else "pair"] += 1
@@ -219,7 +219,7 @@ def test_8b_widths_in_unequal_batches(wide, dtype, monkeypatch):
     monkeypatch.setattr(ops, "gemm_tcgen05_pair", pair)
     monkeypatch.setattr(ops, "attention_prefill_tc", tc)
     monkeypatch.setattr(ops, "gemm_skinny", skinny)
-    monkeypatch.setattr(ops, "attention_decode", dec)
+    monkeypatch.setattr(ops, "attention_decode_fused", dec)
     model = q.build_model(config.plan())
     model.bind({k: v.cuda() for k, v in host.items()}, torch.float32 if dtype == "float32" else torch.bfloat16, "cuda")
     prompt_lengths = dict(zip(requests, WIDE_PROMPTS))
