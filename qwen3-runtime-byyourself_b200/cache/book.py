@@ -114,6 +114,16 @@ class PageGroup:
         for i in range(have, want):
             self.table[slot, i] = self._free.pop()
 
+    def shrink(self, slot: int, length_now: int, n_new: int) -> None:
+        """Undo `extend(slot, length_now, n_new)`: the pages it took go back to the pool."""
+        have = -(-length_now // PAGE_TOKENS)
+        want = -(-(length_now + n_new) // PAGE_TOKENS)
+        for i in range(want - 1, have - 1, -1):
+            page = int(self.table[slot, i])
+            if page >= 0:
+                self._free.append(page)
+                self.table[slot, i] = -1
+
     def trim_window(self, slot: int, length: int) -> None:
         """Give back the pages that no later query of this sequence can read."""
         if self.need.kind != "window":
@@ -219,6 +229,13 @@ class CacheBook:
         for g in self.groups:
             for slot, n_new in step:
                 g.extend(slot, int(self.lengths[slot]), n_new)
+
+    def cancel(self, step: Sequence[Tuple[int, int]]) -> None:
+        """The step did not run after all (its launch failed): the pages that `reserve` took for it go back,
+        lengths stay as they were.  What the failed step may have written lies beyond every length."""
+        for g in self.groups:
+            for slot, n_new in step:
+                g.shrink(slot, int(self.lengths[slot]), n_new)
 
     def commit(self, step: Sequence[Tuple[int, int]]) -> None:
         """The step ran: lengths advance once, window groups return dead pages."""

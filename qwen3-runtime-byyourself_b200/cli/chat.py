@@ -22,52 +22,56 @@ import tempfile
 from typing import List, Optional
 
 USAGE_TAIL = """
-Interactive commands:
-  /exit       Exit the program
-  /quit       Exit the program
-  /clear      Clear conversation history
-  /think on   Enable thinking mode
-  /think off  Disable thinking mode
-  /help       Show interactive help
+While chatting, a line that starts with a slash is a command:
+  /exit, /quit   leave
+  /clear         forget the conversation so far
+  /think on      let the model reason before it answers
+  /think off     ask for the answer straight away
+  /help          this list
 """
 
 
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="qwen3_chat", description="Qwen3 dense generation on one B200.",
                                  epilog=USAGE_TAIL, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("model_directory", nargs="?", metavar="MODEL_DIRECTORY", help="Qwen3 model directory.")
-    ap.add_argument("--model", metavar="PATH", help="Qwen3 model directory.")
-    ap.add_argument("--gpu", type=int, default=0, metavar="INDEX", help="Logical CUDA device index. Default: 0")
+    ap.add_argument("model_directory", nargs="?", metavar="MODEL_DIRECTORY",
+                    help="Folder with config.json, the safetensors and (for text) tokenizer.json.")
+    ap.add_argument("--model", metavar="PATH", help="The same folder, given as an option.")
+    ap.add_argument("--gpu", type=int, default=0, metavar="INDEX", help="Which CUDA device to run on (default 0).")
     ap.add_argument("--max-context", type=int, default=None, metavar="TOKENS",
-                    help="KV cache and RoPE context capacity. Default: 4096")
+                    help="Longest sequence, prompt and answer together, that the cache and the rotation table are sized for "
+                         "(default 4096, never more than the model's own limit).")
     ap.add_argument("--max-new-tokens", type=int, default=512, metavar="TOKENS",
-                    help="Maximum tokens generated per response. Default: 512")
+                    help="Stop an answer after this many new tokens (default 512; less if the context is nearly full).")
     mode = ap.add_mutually_exclusive_group()
     mode.add_argument("--sample", dest="greedy", action="store_false",
-                      help="Use temperature/Top-k/Top-p sampling. This is the default mode.")
-    mode.add_argument("--greedy", dest="greedy", action="store_true", help="Always select the highest-logit token.")
+                      help="Draw each token at random from the filtered distribution (the default).")
+    mode.add_argument("--greedy", dest="greedy", action="store_true",
+                      help="Take the most likely token every time; no randomness.")
     ap.set_defaults(greedy=False)
-    ap.add_argument("--temperature", type=float, default=0.6, metavar="VALUE", help="Sampling temperature. Default: 0.6")
+    ap.add_argument("--temperature", type=float, default=0.6, metavar="VALUE",
+                    help="Logits are divided by this before drawing; above 0 (default 0.6).")
     ap.add_argument("--top-k", type=int, default=20, metavar="VALUE",
-                    help="Top-k sampling size. 0 disables Top-k. Default: 20")
+                    help="Keep only the k best candidates, ties included; 0 keeps all (default 20).")
     ap.add_argument("--top-p", type=float, default=0.95, metavar="VALUE",
-                    help="Top-p probability threshold. 1.0 disables Top-p. Default: 0.95")
-    ap.add_argument("--seed", type=int, default=42, metavar="VALUE", help="Random sampling seed. Default: 42")
+                    help="Keep the smallest set of best candidates whose probability reaches p; 1.0 keeps all (default 0.95).")
+    ap.add_argument("--seed", type=int, default=42, metavar="VALUE",
+                    help="Seed of the random streams; the same seed repeats the same answers (default 42).")
     think = ap.add_mutually_exclusive_group()
     think.add_argument("--thinking", dest="thinking", action="store_true",
-                       help="Enable Qwen3 thinking mode. This is the default.")
+                       help="Let the model write its reasoning before the answer (the default).")
     think.add_argument("--no-thinking", dest="thinking", action="store_false",
-                       help="Prefill an empty thinking block and ask the model to answer directly.")
+                       help="Start the answer after an empty reasoning block, so that the model answers at once.")
     ap.set_defaults(thinking=True)
     show = ap.add_mutually_exclusive_group()
     show.add_argument("--show-thinking", dest="show_thinking", action="store_true",
-                      help="Display the model's thinking content. This is the default.")
+                      help="Print the reasoning as well as the answer (the default).")
     show.add_argument("--hide-thinking", dest="show_thinking", action="store_false",
-                      help="Let the model think, but display only the final answer.")
+                      help="The model may reason, but only the answer is printed.")
     ap.set_defaults(show_thinking=True)
-    ap.add_argument("--system", default="", metavar="TEXT", help="Optional system prompt.")
+    ap.add_argument("--system", default="", metavar="TEXT", help="A system message put before the conversation.")
     ap.add_argument("--stop-token", type=int, action="append", default=[], metavar="ID",
-                    help="Add an extra stop token ID. This option may be repeated.")
+                    help="One more token id that ends an answer, beside the model's own; may be given several times.")
     # additions
     ap.add_argument("--tokens", action="append", default=[], metavar="IDS",
                     help="A prompt as comma-separated token ids; repeat for a batch. Prints token ids.")
@@ -103,17 +107,18 @@ def main(argv: Optional[List[str]] = None) -> int:
     import qwen3_b200 as q
 
     config = q.load_config(args.config if args.random_weights is not None else model_dir)
-    max_context = args.max_context if args.max_context is not None else min(4096, config.max_position_embeddings)
-    if not 0 < max_context <= config.max_position_embeddings:
-        ap.error(f"--max-context must be in 1..{config.max_position_embeddings} (max_position_embeddings)")
-    if args.top_k > config.vocab_size:
+    plan = config.plan()                 # sizes and stop tokens as every architecture states them
+    max_context = args.max_context if args.max_context is not None else min(4096, plan.max_positions)
+    if not 0 < max_context <= plan.max_positions:
+        ap.error(f"--max-context must be in 1..{plan.max_positions} (the model's longest sequence)")
+    if args.top_k > plan.vocab_size:
         ap.error("--top-k exceeds the vocabulary size")
     sampling = (q.SamplingParams(mode="greedy") if args.greedy else
                 q.SamplingParams(mode="sample", temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                                  seed=args.seed))
-    stops = sorted({config.eos_token_id, config.bos_token_id, *args.stop_token})
+    stops = sorted({*plan.stop_token_ids, *args.stop_token})
     for s in stops:
-        if not 0 <= s < config.vocab_size:
+        if not 0 <= s < plan.vocab_size:
             ap.error(f"stop token {s} is outside the vocabulary")
 
     prompts = [parse_ids(t) for t in args.tokens]
@@ -147,7 +152,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     from .chat_template import apply_chat_template, split_thinking
     from .tokenizer import Tokenizer
     tokenizer = Tokenizer.load(tokenizer_path)
-    if tokenizer.vocab_size > config.vocab_size:
+    if tokenizer.vocab_size > plan.vocab_size:
         ap.error("the tokenizer has more ids than the model's vocabulary")
     sampling = q.SamplingParams(**{**sampling.__dict__, "valid_vocab_size": tokenizer.vocab_size})
     engine = make_engine()

@@ -20,7 +20,7 @@
 
 namespace {
 
-constexpr int PAGE = 64;
+constexpr int PAGE = Q3_PAGE_TOKENS;
 constexpr int MAX_HEAD_DIM = 256;
 
 template <typename T> __device__ __forceinline__ void load_pack_f32(const T* p, float (&v)[Pack<T>::N]) {

@@ -29,7 +29,8 @@
 namespace {
 
 constexpr int D = Q3_HEAD_DIM;
-constexpr int PAGE = 64;
+constexpr int PAGE = Q3_PAGE_TOKENS;
+static_assert(PAGE == 64, "the decode attention gives each of its four warps 16 keys of a page");
 constexpr int WARPS = 4;
 constexpr int KEYS_PER_WARP = PAGE / WARPS;        // 16
 constexpr int ROW_BYTES = D * 2 + 16;              // padded row: ldmatrix reads without bank conflicts
@@ -452,11 +453,10 @@ Q3_EXPORT int q3_attention_decode_bf16(const void* q, const void* k_pages, const
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || n_splits <= 0) return Q3_ERR_BAD_SIZE;
     if (n_tokens > 65535 || nkv > 65535) return Q3_ERR_TOO_LARGE;
     cudaStream_t stream = (cudaStream_t)stream_;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    static Q3PerDevice configured;
+    {
+        cudaError_t e = q3_allow_shared_memory(decode_split_kernel<false>, SMEM_BYTES, configured);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     float* part_o = scratch;
     float* part_ml = scratch + n_tokens * nq * n_splits * D;
@@ -482,16 +482,9 @@ Q3_EXPORT int q3_attention_decode_fused_bf16(const void* qkv, void* k_pages, voi
     if (n_tokens > 65535 || nkv > 65535) return Q3_ERR_TOO_LARGE;
     if (!aligned16(qkv) || !aligned16(k_pages) || !aligned16(v_pages)) return Q3_ERR_MISALIGNED;
     cudaStream_t stream = (cudaStream_t)stream_;
-    static bool configured[64] = {false};
-    int device = 0;
-    cudaError_t e = cudaGetDevice(&device);
+    static Q3PerDevice configured;
+    cudaError_t e = q3_allow_shared_memory(decode_split_kernel<true>, SMEM_FUSED, configured);
     if (e != cudaSuccess) return (int)e;
-    if (device < 0 || device >= 64) return Q3_ERR_BAD_SIZE;
-    if (!configured[device]) {
-        e = cudaFuncSetAttribute(decode_split_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_FUSED);
-        if (e != cudaSuccess) return (int)e;
-        configured[device] = true;
-    }
     FusedArgs fused;
     fused.qkv = (const bf16*)qkv;
     fused.out = (bf16*)out;

@@ -24,7 +24,8 @@
 namespace {
 
 constexpr int D = Q3_HEAD_DIM;
-constexpr int PAGE = 64;
+constexpr int PAGE = Q3_PAGE_TOKENS;
+static_assert(PAGE == 64, "the tiled prompt attention takes one page of 64 keys per step");
 constexpr int BM = 64;                              // query rows per block
 constexpr int WARPS = 4;
 constexpr int ROW_BYTES = D * 2 + 16;               // padded rows: conflict-free ldmatrix
@@ -227,11 +228,10 @@ Q3_EXPORT int q3_attention_prefill_bf16(const void* q, const void* k_pages, cons
     if (n_seqs <= 0 || max_new <= 0) return 0;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0) return Q3_ERR_BAD_SIZE;
     if (n_seqs > 65535 || nq > 65535) return Q3_ERR_TOO_LARGE;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    static Q3PerDevice configured;
+    {
+        cudaError_t e = q3_allow_shared_memory(prefill_kernel, SMEM_BYTES, configured);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     const dim3 grid((max_new + BM - 1) / BM, nq, n_seqs);
     return (int)q3_launch(prefill_kernel, grid, dim3(WARPS * 32), SMEM_BYTES, (cudaStream_t)stream, (const bf16*)q,

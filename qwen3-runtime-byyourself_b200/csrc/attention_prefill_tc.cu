@@ -22,6 +22,8 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
+#include "tma.cuh"
 
 #ifndef Q3_HEAD_DIM
 #error "compile with -DQ3_HEAD_DIM=<64 or 128>"
@@ -31,7 +33,8 @@ namespace {
 
 constexpr int D = Q3_HEAD_DIM;
 static_assert(D == 64 || D == 128, "the tcgen05 attention takes head sizes 64 and 128");
-constexpr int PAGE = 64, BM = 128, HALVES = D / 64;
+constexpr int PAGE = Q3_PAGE_TOKENS, BM = 128, HALVES = D / 64;
+static_assert(PAGE == 64, "the tcgen05 prompt attention takes one page of 64 keys per product");
 constexpr int THREADS = 224;
 constexpr int K_STAGES = 3, V_STAGES = 2;                // pages of K and of V in flight or in use
 constexpr int Q_BYTES = HALVES * BM * 128;               // 128 rows x 128 bytes per half
@@ -41,54 +44,8 @@ constexpr int PANEL_BYTES = HALVES * PAGE * 128;         // one page of K (or V)
 constexpr int SMEM_BYTES = Q_BYTES + (K_STAGES + V_STAGES) * PANEL_BYTES + 256;
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t COL_S = 0, COL_P = 64, COL_O = 128;
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
 constexpr float RESCALE_THRESHOLD = 8.0f;                // in log2 units: probabilities stay below 2^8
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.b32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// D[tmem] (+)= A[smem] . B[smem]
-__device__ __forceinline__ void tc_mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
-}
-// D[tmem] (+)= A[tmem] . B[smem]
-__device__ __forceinline__ void tc_mma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
-}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
@@ -108,21 +65,6 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* r) {
           "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
           "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// K-major operand (rows of 128 bytes, 128-byte swizzle, eight-row groups 1024 bytes apart).
-__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
-    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
-           ((uint64_t)2 << 61);
-}
-// MN-major operand: 64 contiguous elements of the N dimension per 128-byte row, one row per k;
-// eight-k groups 1024 bytes apart (stride offset), the next 64 elements of N `chunk_bytes` further
-// (leading offset).
-__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t chunk_bytes) {
-    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((chunk_bytes >> 4) & 0x3FFFu) << 16) |
-           ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 // kind::f16 instruction descriptor: float32 accumulator, bfloat16 operands; bit 16 = B is MN-major.
 constexpr uint32_t idesc(int m, int n, bool b_mn_major) {
@@ -386,35 +328,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)p;
-    }
-    return fn;
-}
-
-// [rows, cols] bfloat16 row-major, fetched in boxes of [box_rows, 64 columns] with 128-byte swizzle.
-bool make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int box_rows) {
-    EncodeTiled fn = encode_fn();
-    if (fn == nullptr) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 }  // namespace
 
 Q3_EXPORT int q3_attention_prefill_tc_head_dim() { return D; }
@@ -428,15 +341,14 @@ Q3_EXPORT int q3_attention_prefill_tc_bf16(const void* q, const void* k_pages, c
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || !(scale > 0.0f)) return Q3_ERR_BAD_SIZE;   // the row maximum is taken before scaling
     if (n_seqs > 65535 || nq > 65535) return Q3_ERR_TOO_LARGE;
     if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(out)) return Q3_ERR_MISALIGNED;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    static Q3PerDevice configured;
+    {
+        cudaError_t e = q3_allow_shared_memory(prefill_tc_kernel, SMEM_BYTES, configured);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     CUtensorMap map_q, map_k, map_v;
-    if (!make_map(&map_q, q, n_tokens, (int64_t)nq * D, BM) || !make_map(&map_k, k_pages, n_cache_pages * nkv * PAGE, D, PAGE) ||
-        !make_map(&map_v, v_pages, n_cache_pages * nkv * PAGE, D, PAGE))
+    if (!q3_make_map_bf16(&map_q, q, n_tokens, (int64_t)nq * D, BM, 64, true) || !q3_make_map_bf16(&map_k, k_pages, n_cache_pages * nkv * PAGE, D, PAGE, 64, true) ||
+        !q3_make_map_bf16(&map_v, v_pages, n_cache_pages * nkv * PAGE, D, PAGE, 64, true))
         return Q3_ERR_BAD_SIZE;
     const dim3 grid((max_new + BM - 1) / BM, nq, n_seqs);
     return (int)q3_launch(prefill_tc_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)stream, map_q, map_k, map_v,

@@ -27,6 +27,12 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "--expt-relaxed-constexpr"]
 
+def _page_define() -> str:
+    """The cache's page size, handed to every kernel source: one constant, in cache/book.py."""
+    from ..cache.book import PAGE_TOKENS
+    return f"Q3_PAGE_TOKENS={PAGE_TOKENS}"
+
+
 _loaded: Dict[Tuple[str, Tuple[str, ...]], ctypes.CDLL] = {}
 _lock = threading.Lock()
 
@@ -85,7 +91,7 @@ def _digest(source: str, defines: Tuple[str, ...], extra: Tuple[str, ...]) -> st
     for name in _sources_of(source):
         with open(os.path.join(HERE, name), "rb") as f:
             h.update(f.read())
-    h.update(repr((defines, extra, ARCH_FLAGS, BASE_FLAGS)).encode())
+    h.update(repr((defines, extra, ARCH_FLAGS, BASE_FLAGS, _page_define())).encode())
     return h.hexdigest()[:12]
 
 
@@ -104,7 +110,7 @@ def compile_library(source: str, defines: Iterable[str] = (), extra_flags: Itera
         return out
     nvcc = find_nvcc()
     tmp = f"{out}.{os.getpid()}.tmp"
-    cmd = [nvcc, *ARCH_FLAGS, *BASE_FLAGS, *extra, *[f"-D{d}" for d in defines], "-I", HERE,
+    cmd = [nvcc, *ARCH_FLAGS, *BASE_FLAGS, *extra, f"-D{_page_define()}", *[f"-D{d}" for d in defines], "-I", HERE,
            "-o", tmp, os.path.join(HERE, source)]
     label = source + (" [" + " ".join(defines) + "]" if defines else "")
     if verbose:

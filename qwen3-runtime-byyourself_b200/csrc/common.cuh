@@ -12,6 +12,38 @@ typedef __nv_bfloat16 bf16;
 
 #define Q3_EXPORT extern "C" __attribute__((visibility("default")))
 
+// Tokens per page of the key/value cache.  The build passes the cache's own constant
+// (-DQ3_PAGE_TOKENS=<cache.book.PAGE_TOKENS>); the attention kernels are tiled for 64.
+#ifndef Q3_PAGE_TOKENS
+#define Q3_PAGE_TOKENS 64
+#endif
+
+// Multiprocessors of the current device (asked once per device).
+static inline int q3_device_sm_count() {
+    static int counts[64] = {0};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 1;
+    if (counts[device] == 0) cudaDeviceGetAttribute(&counts[device], cudaDevAttrMultiProcessorCount, device);
+    return counts[device] > 0 ? counts[device] : 1;
+}
+
+// Raises a kernel's limit of dynamic shared memory, once per device (the attribute belongs to the device's
+// copy of the kernel).  `done` is a static array of the call site.
+struct Q3PerDevice {
+    bool done[64] = {};
+};
+template <typename Kernel>
+static inline cudaError_t q3_allow_shared_memory(Kernel kernel, int bytes, Q3PerDevice& state) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    if (state.done[device]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) state.done[device] = true;
+    return e;
+}
+
 // Error codes of argument checks, above the cudaError_t range.
 #define Q3_ERR_BAD_SIZE 10001
 #define Q3_ERR_TOO_LARGE 10002

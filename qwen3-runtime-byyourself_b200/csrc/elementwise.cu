@@ -233,7 +233,8 @@ static int silu_mul_launch(const T* gate_up, T* out, int64_t rows, int inter, in
     const int threads = 256;
     const int64_t work = rows * (inter / (vec ? V : 1));
     int64_t blocks = (work + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    const int64_t resident = (int64_t)q3_device_sm_count() * 16;       // blocks of 128 threads an SM holds
+    if (blocks > resident) blocks = resident;
     if (vec)
         return (int)q3_launch(silu_mul_kernel<T, V>, dim3((unsigned)blocks), dim3(threads), 0, stream, gate_up, out, rows,
                               inter, interleaved);

@@ -166,12 +166,10 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT*
 template <int MT, int R, int WARPS, int PF, int MINB, bool GATED, typename OutT>
 int launch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, cudaStream_t stream) {
     constexpr int SMEM = WARPS * 8 * MT * (16 * R + 1) * 4;
-    static bool configured = false;
-    if (SMEM > 48 * 1024 && !configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, R, WARPS, PF, MINB, GATED, OutT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    static Q3PerDevice configured;
+    if (SMEM > 48 * 1024) {
+        cudaError_t e = q3_allow_shared_memory(gemm_skinny_kernel<MT, R, WARPS, PF, MINB, GATED, OutT>, SMEM, configured);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     const int blocks = (N + 16 * R - 1) / (16 * R);
     return (int)q3_launch(gemm_skinny_kernel<MT, R, WARPS, PF, MINB, GATED, OutT>, dim3(blocks), dim3(WARPS * 32), SMEM,

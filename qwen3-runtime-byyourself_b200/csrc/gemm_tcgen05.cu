@@ -27,6 +27,8 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
+#include "tma.cuh"
 
 namespace {
 
@@ -34,47 +36,8 @@ constexpr int BM = 128;                 // rows of W per tile (the UMMA M)
 constexpr int BK = 64;                  // K per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr uint32_t Q3_WAIT_LIMIT = 1u << 24;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// Bounded wait: true if the phase completed, false if the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < Q3_WAIT_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.b32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    tc_mma_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
 }
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -83,15 +46,8 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr) : "memory");
 }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, groups of
-// eight rows 1024 bytes apart.  Bits: [0,14) address>>4, [16,30) leading offset>>4 (unused for
-// swizzled K-major, 1), [32,46) stride offset>>4, [46,48) version 1, [61,64) layout 2 (128B).
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) { return desc_k_major(smem_addr); }
 
 // Instruction descriptor of kind::f16: float32 accumulator, bfloat16 A and B, both K-major.
 __host__ __device__ constexpr uint32_t make_idesc(int n) {
@@ -690,44 +646,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     }
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)p;
-    }
-    return fn;
-}
-
 // A [rows, K] bfloat16 row-major matrix, fetched in boxes of [box_rows, 64] with 128-byte swizzle.
 bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
-    EncodeTiled fn = encode_fn();
-    if (fn == nullptr) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return q3_make_map_bf16(map, ptr, rows, K, box_rows, BK, true);
 }
 
-int sm_count() {
-    static int count = 0;
-    if (count == 0) {
-        int device = 0;
-        cudaGetDevice(&device);
-        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
-    }
-    return count;
-}
+int sm_count() { return q3_device_sm_count(); }
 
 // K ranges (blocks per cluster) for a matrix of N rows: the largest power of two up to the portable
 // cluster size that keeps the grid within 2.6 blocks per SM (two are resident; more blocks than that keep
@@ -745,12 +669,10 @@ int mid_splits(int N, int K, int token_tiles) {
 template <int MT, int STAGES, int MINB, bool GATED, typename OutT>
 int launch_mid(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int splits, int* status, cudaStream_t stream) {
     constexpr int SMEM = STAGES * (BM * BK * 2 + MT * BK * 2) + 1024 + 256;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_mid_kernel<MT, STAGES, MINB, GATED, OutT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    static Q3PerDevice configured;
+    {
+        cudaError_t e = q3_allow_shared_memory(gemm_tcgen05_mid_kernel<MT, STAGES, MINB, GATED, OutT>, SMEM, configured);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     CUtensorMap map_w, map_x;
     if (!make_map(&map_w, W, N, K, BM) || !make_map(&map_x, X, M, K, MT)) return Q3_ERR_BAD_SIZE;
@@ -778,12 +700,10 @@ int dispatch_mid(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int
 template <int BN, int STAGES, bool GATED, typename OutT>
 int launch_prompt(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int* status, cudaStream_t stream) {
     constexpr int SMEM = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_prompt_kernel<BN, STAGES, GATED, OutT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    static Q3PerDevice configured;
+    {
+        cudaError_t e = q3_allow_shared_memory(gemm_tcgen05_prompt_kernel<BN, STAGES, GATED, OutT>, SMEM, configured);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     CUtensorMap map_x, map_w;
     if (!make_map(&map_x, X, M, K, BM) || !make_map(&map_w, W, N, K, BN)) return Q3_ERR_BAD_SIZE;
@@ -796,12 +716,10 @@ int launch_prompt(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, in
 template <int STAGES, bool GATED, typename OutT>
 int launch_pair(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int* status, cudaStream_t stream) {
     constexpr int SMEM = STAGES * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<STAGES, GATED, OutT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    static Q3PerDevice configured;
+    {
+        cudaError_t e = q3_allow_shared_memory(gemm_tcgen05_pair_kernel<STAGES, GATED, OutT>, SMEM, configured);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     CUtensorMap map_x, map_w;
     if (!make_map(&map_x, X, M, K, BM) || !make_map(&map_w, W, N, K, 128)) return Q3_ERR_BAD_SIZE;

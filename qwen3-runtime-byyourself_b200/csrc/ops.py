@@ -14,6 +14,7 @@ from typing import Optional
 
 import torch
 
+from ..cache.book import PAGE_TOKENS
 from .build import load_library
 
 _ERRORS = {10001: "a size the kernel does not take", 10002: "more rows than one launch takes",
@@ -223,7 +224,7 @@ def qkv_prepare(qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, cos, sin, toke
     s = _suffix(qkv)
     if d % 16 != 0 or d > 256:
         raise KernelError(f"head_dim {d} is not supported: multiples of 16 up to 256")
-    if qkv.shape[-1] != (nq + 2 * nkv) * d or k_pages.dtype != qkv.dtype or k_pages.shape[1:] != (nkv, 64, d):
+    if qkv.shape[-1] != (nq + 2 * nkv) * d or k_pages.dtype != qkv.dtype or k_pages.shape[1:] != (nkv, PAGE_TOKENS, d):
         raise KernelError("qkv_prepare: shapes do not fit")
     fn = _fn("attention.cu", f"q3_qkv_prepare_{s}",
              [c_void_p] * 11 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_void_p])
@@ -321,7 +322,7 @@ def attention_decode_fused(qkv, k_pages, v_pages, out, q_norm_w, k_norm_w, cos, 
         raise KernelError("attention_decode_fused is a bfloat16 kernel")
     if nq // nkv > 16 or d % 16 != 0 or d > 256 or not 0 < n_splits <= FUSED_DECODE_MAX_SPLITS:
         raise KernelError(f"attention_decode_fused: group of {nq // nkv} heads, head_dim {d} or {n_splits} splits not supported")
-    if qkv.shape[-1] != (nq + 2 * nkv) * d or k_pages.shape[1:] != (nkv, 64, d) or out.shape[-1] != nq * d:
+    if qkv.shape[-1] != (nq + 2 * nkv) * d or k_pages.shape[1:] != (nkv, PAGE_TOKENS, d) or out.shape[-1] != nq * d:
         raise KernelError("attention_decode_fused: shapes do not fit")
     fn = _fn("attention_decode.cu", "q3_attention_decode_fused_bf16",
              [c_void_p] * 8 + [c_float] + [c_void_p] * 3 + [c_int, c_int64, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
@@ -419,7 +420,6 @@ def gemm_tcgen05_mid(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits
 
 def gemm_tcgen05_mid_splits(M: int, N: int, K: int) -> int:
     """The number of K ranges `gemm_tcgen05_mid` chooses for this shape."""
-    from .build import load_library
     lib = load_library("gemm_tcgen05.cu", ())
     lib.q3_gemm_tcgen05_mid_splits.argtypes = [c_int, c_int, c_int]
     lib.q3_gemm_tcgen05_mid_splits.restype = c_int

@@ -523,19 +523,13 @@ Q3_EXPORT int q3_sample_f32(const float* logits, int64_t stride, int rows, int v
     if (rows <= 0) return 0;
     if (valid <= 0 || valid > stride || !(temperature > 0.0f) || top_k < 0 || !(top_p > 0.0f && top_p <= 1.0f))
         return Q3_ERR_BAD_SIZE;
-    static bool configured = false;
-    if (!configured) {              // static and dynamic shared memory together pass the default limit of 48 KB
-        cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRIVATE_BYTES);
+    static Q3PerDevice configured;              // static and dynamic shared memory together pass the default limit of 48 KB
+    {
+        cudaError_t e = q3_allow_shared_memory(sample_kernel, PRIVATE_BYTES, configured);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     // blocks per row: as many as keep the clusters of all rows resident at once (one block of 1,024 threads an SM)
-    static int sms = 0;
-    if (sms == 0) {
-        int device = 0;
-        cudaGetDevice(&device);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    }
+    const int sms = q3_device_sm_count();
     int n_blocks = S_BLOCKS_MAX;
     while (n_blocks > 1 && (int64_t)rows * n_blocks > sms) n_blocks >>= 1;
     return (int)q3_launch_cluster(sample_kernel, dim3(rows * n_blocks), dim3(S_THREADS), PRIVATE_BYTES, (cudaStream_t)stream,

@@ -68,7 +68,7 @@ static inline Q3EncodeTiled q3_encode_fn() {
 // A [rows, K] bfloat16 row-major matrix fetched in boxes of [box_rows, box_cols]; outside the matrix a
 // box reads zeros.  `swizzle128`: rows of 64 elements whose 16-byte chunks are XOR-ed with the row index
 // (the layout the tcgen05 operand descriptors expect); otherwise the box lands dense, row after row.
-static inline bool q3_make_map_bf16(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows, int box_cols,
+static inline bool q3_make_map_bf16(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows, int box_cols,
                                     bool swizzle128) {
     Q3EncodeTiled fn = q3_encode_fn();
     if (fn == nullptr) return false;
@@ -79,13 +79,4 @@ static inline bool q3_make_map_bf16(CUtensorMap* map, const void* ptr, int rows,
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-// Multiprocessors of the current device, asked once per device.
-static inline int q3_sm_count() {
-    static int counts[64] = {0};
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 1;
-    if (counts[device] == 0) cudaDeviceGetAttribute(&counts[device], cudaDevAttrMultiProcessorCount, device);
-    return counts[device] > 0 ? counts[device] : 1;
 }

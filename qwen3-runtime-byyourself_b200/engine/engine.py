@@ -332,19 +332,23 @@ class Engine:
             raise StepError("device_tokens stand for one token per entry")
         step = list(zip(slots, n_new))
         self.cache.reserve(step)                            # raises before anything is launched
-        pos0 = [self.cache.length(s) for s in slots]
-        token_ids = np.concatenate(tokens)
-        if decode and self.use_graphs:
-            logits = self._step_captured(slots, pos0, token_ids, want_rows, device_tokens)
-        else:
-            from ..csrc import ops
-            before = ops.launch_count()
-            ctx = self._build_context(slots, n_new, pos0, token_ids, want_rows)
-            if device_tokens is not None:
-                ctx.token_ids[:len(slots)].copy_(device_tokens)
-            with ops.on_current_stream():
-                logits = self.model.forward(ctx, self.cache)
-            self.launches += ops.launch_count() - before
+        try:
+            pos0 = [self.cache.length(s) for s in slots]
+            token_ids = np.concatenate(tokens)
+            if decode and self.use_graphs:
+                logits = self._step_captured(slots, pos0, token_ids, want_rows, device_tokens)
+            else:
+                from ..csrc import ops
+                before = ops.launch_count()
+                ctx = self._build_context(slots, n_new, pos0, token_ids, want_rows)
+                if device_tokens is not None:
+                    ctx.token_ids[:len(slots)].copy_(device_tokens)
+                with ops.on_current_stream():
+                    logits = self.model.forward(ctx, self.cache)
+                self.launches += ops.launch_count() - before
+        except BaseException:
+            self.cache.cancel(step)                         # a kernel refused its sizes, memory ran out: the pages go back
+            raise
         self.cache.commit(step)
         return logits
 

@@ -69,6 +69,28 @@ def test_a_step_that_does_not_fit_changes_nothing():
     assert np.array_equal(before, book.groups[0].table) and book.groups[0].n_free == 2
 
 
+def test_a_cancelled_step_gives_its_pages_back_and_can_be_tried_again():
+    window = CacheNeed("window", 1, 16, window=70)
+    book = CacheBook([FULL, window], max_tokens=6 * PAGE_TOKENS, max_seq_len=5 * PAGE_TOKENS)
+    a, b = book.alloc_slot(), book.alloc_slot()
+    book.reserve([(a, 100), (b, 3)])
+    book.commit([(a, 100), (b, 3)])
+    tables = [g.table.copy() for g in book.groups]
+    free = [sorted(g._free) for g in book.groups]
+    step = [(a, 130), (b, 62)]                  # two more pages for a (three in the window group's count too), one for b
+    book.reserve(step)
+    assert all(g.n_free < len(f) for g, f in zip(book.groups, free))
+    book.cancel(step)
+    assert book.length(a) == 100 and book.length(b) == 3
+    for g, t, f in zip(book.groups, tables, free):
+        assert np.array_equal(g.table, t) and sorted(g._free) == f
+    book.reserve(step)                          # the same step again: nothing was lost, so it still fits
+    book.commit(step)
+    assert book.length(a) == 230 and book.length(b) == 65
+    book.free_slot(a); book.free_slot(b)
+    assert all(g.n_free == g.n_pages for g in book.groups)
+
+
 def test_random_schedule_never_loses_or_doubles_a_page():
     rng = np.random.default_rng(0)
     book = CacheBook([FULL, FULL], max_tokens=40 * PAGE_TOKENS, max_seq_len=9 * PAGE_TOKENS, n_slots=8)
@@ -88,6 +110,9 @@ def test_random_schedule_never_loses_or_doubles_a_page():
             try:
                 book.reserve(step)
             except CacheFull:
+                continue
+            if rng.random() < 0.15:             # the step's launch failed: what was reserved goes back
+                book.cancel(step)
                 continue
             book.commit(step)
             for s, n in step:

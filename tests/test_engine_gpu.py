@@ -196,7 +196,22 @@ def test_step_errors_leave_the_cache_unchanged(folders):
     assert engine.length(s) == 0 and engine.cache.pages_held() == 0
     assert engine.step([StepEntry(s, [1, 2, 3], [])]) is None
     assert engine.length(s) == 3
+    # a failure after the pages were reserved (a kernel that refuses its sizes, memory that runs out while the
+    # scratch grows): the pages go back, the length stays, and the same step then runs
+    held, real_forward = engine.cache.pages_held(), engine.model.forward
+
+    def failing(ctx, cache):
+        raise RuntimeError("launch failed")
+
+    engine.model.forward = failing
+    with pytest.raises(RuntimeError, match="launch failed"):
+        engine.step([StepEntry(s, list(range(70)), [69])])
+    engine.model.forward = real_forward
+    assert engine.length(s) == 3 and engine.cache.pages_held() == held
+    assert engine.step([StepEntry(s, list(range(70)), [69])]).shape == (1, 256)
+    assert engine.length(s) == 73 and engine.cache.pages_held() == 2
     engine.release(s)
+    assert engine.cache.pages_held() == 0
 
 
 def test_8b_layer_shapes_in_32_bit_match_the_plain_model():
