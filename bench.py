@@ -236,6 +236,41 @@ def e2e_run(q, engine, torch, rng, batch, longest_prompt, steps, warmup):
             "host_ms": busy[0] / max(busy[1], 1) * 1e3}
 
 
+def kernel_breakdown(q, engine, sampler, torch, rng, batch, context, cfg, layers):
+    """Microseconds per entry point of this library's kernels in one decode step of the headline batch and in
+    one prompt step of 2,048 tokens, from CUDA events around every launch."""
+    from qwen3_b200.csrc import ops
+    engine.use_graphs = False                       # every kernel launched by itself, so that each can be timed
+    lengths = unequal_lengths(batch, context - 8, rng)
+    slots = [engine.new_sequence() for _ in range(batch)]
+    chunk = max(1, 8192 // max(lengths))
+    for lo in range(0, batch, chunk):
+        part = range(lo, min(batch, lo + chunk))
+        engine.step([q.StepEntry(slots[i], rng.integers(0, engine.vocab_size, size=lengths[i]).tolist(), []) for i in part])
+    entries = [q.StepEntry(s, [1], [0]) for s in slots]
+    out = {"config": {"layers": layers, "batch": batch, "context": context, "prompt_tokens": PREFILL_TOKENS}}
+    for _ in range(2):
+        sampler.choose_device(engine.step(entries), list(range(batch)), [0] * batch)
+    with ops.KernelTimer() as timer:
+        sampler.choose_device(engine.step(entries), list(range(batch)), [0] * batch)
+    out["decode_step_us"] = {k: [n, round(us, 1)] for k, (n, us) in sorted(timer.summary().items())}
+    out["decode_step_total_us"] = round(sum(us for _, us in timer.summary().values()), 1)
+    for s in slots:
+        engine.release(s)
+    prompt = rng.integers(0, engine.vocab_size, size=PREFILL_TOKENS).tolist()
+    for rep in range(3):
+        slot = engine.new_sequence()
+        if rep < 2:
+            engine.step([q.StepEntry(slot, prompt, [PREFILL_TOKENS - 1])])
+        else:
+            with ops.KernelTimer() as timer:
+                engine.step([q.StepEntry(slot, prompt, [PREFILL_TOKENS - 1])])
+        engine.release(slot)
+    out["prompt_step_us"] = {k: [n, round(us, 1)] for k, (n, us) in sorted(timer.summary().items())}
+    out["prompt_step_total_us"] = round(sum(us for _, us in timer.summary().values()), 1)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -247,6 +282,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=None, help="default: the shape's own (8b: 8, 14b: 16, 32b: 8)")
     ap.add_argument("--context", type=int, default=None, help="default: the shape's own (8b: 4096, 14b: 8192, 32b: 16384)")
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
+    ap.add_argument("--kernels", action="store_true",
+                    help="instead of the benchmark: time every kernel of one decode step and of one 2,048-token prompt step "
+                         "with CUDA events (steps launched afresh, not replayed) and print the sums per entry point")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -276,6 +314,10 @@ def main() -> int:
     engine = q.Engine.from_random(config, seed=0, dtype="bfloat16", max_tokens=max_batch * CONTEXT,
                                   max_seq_len=CONTEXT)
     sampler = Sampler(q.SamplingParams(mode="greedy"), engine.vocab_size, engine.device)
+
+    if args.kernels:
+        print(json.dumps(kernel_breakdown(q, engine, sampler, torch, rng, batch, CONTEXT, cfg, layers)))
+        return 0
 
     # headline: batch 8 whose longest sequence ends at the context length
     clocks = ClockSampler()

@@ -237,6 +237,10 @@ class Qwen3Config:
     # -- the model as data
     def plan(self) -> ModelPlan:
         H, d, eps = self.hidden_size, self.head_dim, self.rms_norm_eps
+        if d % 16 != 0 or d > 256:
+            # config.json allows any even head size (src/model/config.cpp:205-209); this library's attention
+            # kernels are tiled in steps of 16, so the model is refused here, before any weight is read
+            raise ConfigError(f"head_dim {d}: this library runs head sizes that are multiples of 16, up to 256")
         norm = PartSpec("rms_norm", {"size": H, "eps": eps})
         mixer = PartSpec("gqa_attention", {
             "hidden_size": H,

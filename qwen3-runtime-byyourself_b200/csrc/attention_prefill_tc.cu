@@ -87,13 +87,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __global__ void __launch_bounds__(THREADS)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ seq_start,
-                  const int* __restrict__ seq_pos0, const int* __restrict__ page_table, int pages_per_seq, int nq, int nkv,
-                  float scale_log2, int* __restrict__ status) {
+                  const int* __restrict__ seq_pos0, const int* __restrict__ page_table, int pages_per_seq, int n_seqs,
+                  int n_tiles, int nq, int nkv, float scale_log2, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
     pdl_launch_dependents();
     pdl_wait();
-    // the last tiles of a sequence see the most keys: they are scheduled first
-    const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
+    // Blocks start in the order of their index, so the index runs over the tiles from last to first, and for
+    // each tile over every sequence and head: the tiles that see the most keys start first on all SMs, and
+    // the short ones fill the gaps at the end (with the heads of one sequence side by side, the last heads'
+    // long tiles would start when the GPU is nearly done).
+    const int tile = n_tiles - 1 - (int)(blockIdx.x / (unsigned)(n_seqs * nq));
+    const int seq = (int)(blockIdx.x / (unsigned)nq) % n_seqs, head = (int)(blockIdx.x % (unsigned)nq);
     const int t0 = seq_start[seq], n_new = seq_start[seq + 1] - t0;
     if (tile * BM >= n_new) return;
     const int kvh = head / (nq / nkv);
@@ -350,8 +354,10 @@ Q3_EXPORT int q3_attention_prefill_tc_bf16(const void* q, const void* k_pages, c
     if (!q3_make_map_bf16(&map_q, q, n_tokens, (int64_t)nq * D, BM, 64, true) || !q3_make_map_bf16(&map_k, k_pages, n_cache_pages * nkv * PAGE, D, PAGE, 64, true) ||
         !q3_make_map_bf16(&map_v, v_pages, n_cache_pages * nkv * PAGE, D, PAGE, 64, true))
         return Q3_ERR_BAD_SIZE;
-    const dim3 grid((max_new + BM - 1) / BM, nq, n_seqs);
-    return (int)q3_launch(prefill_tc_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)stream, map_q, map_k, map_v,
-                          (bf16*)out, seq_start, seq_pos0, page_table, pages_per_seq, nq, nkv, scale * 1.4426950408889634f,
-                          status);
+    const int n_tiles = (max_new + BM - 1) / BM;
+    const int64_t blocks = (int64_t)n_tiles * n_seqs * nq;
+    if (blocks > 0x7fffffff) return Q3_ERR_TOO_LARGE;
+    return (int)q3_launch(prefill_tc_kernel, dim3((unsigned)blocks), dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)stream, map_q,
+                          map_k, map_v, (bf16*)out, seq_start, seq_pos0, page_table, pages_per_seq, n_seqs, n_tiles, nq, nkv,
+                          scale * 1.4426950408889634f, status);
 }

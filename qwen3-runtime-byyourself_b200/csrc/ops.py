@@ -42,7 +42,60 @@ def set_pdl(on: bool) -> None:
         lib.q3_set_pdl(int(_pdl))
 
 
+class KernelTimer:
+    """Times every launch of this library with a pair of CUDA events while it is active:
+
+        with ops.KernelTimer() as timer:
+            engine.step(...)
+        timer.summary()  ->  {entry point: (launches, total microseconds)}
+
+    For steps that are launched afresh (a captured step is one replay and shows nothing).  The events add a
+    few microseconds of host work per launch, so the step as a whole runs slower than untimed; the
+    durations are those of the kernels."""
+
+    def __init__(self):
+        self.records = []
+
+    def __enter__(self):
+        global _timer
+        self._before, _timer = _timer, self
+        return self
+
+    def __exit__(self, *exc):
+        global _timer
+        _timer = self._before
+        return False
+
+    def run(self, name, fn, args):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream = torch.cuda.ExternalStream(_stream()) if _stream() else torch.cuda.current_stream()
+        start.record(stream)
+        code = fn(*args)
+        stop.record(stream)
+        self.records.append((name, start, stop))
+        return code
+
+    def summary(self) -> dict:
+        torch.cuda.synchronize()
+        out = {}
+        for name, start, stop in self.records:
+            n, us = out.get(name, (0, 0.0))
+            out[name] = (n + 1, us + start.elapsed_time(stop) * 1e3)
+        return out
+
+
+_timer: Optional[KernelTimer] = None
+
+
 def _fn(source: str, name: str, argtypes, defines=()):
+    fn = _fn_untimed(source, name, argtypes, defines)
+    if _timer is None:
+        return fn
+    timer = _timer
+    return lambda *args: timer.run(name, fn, args)
+
+
+def _fn_untimed(source: str, name: str, argtypes, defines=()):
     key = (source, name, tuple(defines))
     fn = _fn_cache.get(key)
     if fn is None:

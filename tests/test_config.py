@@ -205,3 +205,16 @@ def test_plan_checks_order_and_cache_sharing():
     assert shared.layers[1].cache_from == 0
     with pytest.raises(ValueError):
         dataclasses.replace(plan, layers=[dataclasses.replace(plan.layers[0], cache_from=1), plan.layers[1]])
+
+
+def test_a_head_size_the_kernels_do_not_take_is_refused_when_the_model_is_planned():
+    """config.json may hold any even head size (the reference's own rule), so parsing accepts it; the plan,
+    which is the first thing an engine asks for, says what this library runs."""
+    import qwen3_b200 as q
+    cfg = dict(tiny("A"), head_dim=24)
+    config = q.config_from_dict(cfg)
+    assert config.head_dim == 24
+    with pytest.raises(q.ConfigError, match="multiples of 16"):
+        config.plan()
+    with pytest.raises(q.ConfigError, match="multiples of 16"):
+        q.config_from_dict(dict(cfg, head_dim=272)).plan()
