@@ -266,6 +266,46 @@ static int gather_rows_launch(const T* x, const T* delta, const int* idx, T* out
     return (int)q3_launch(gather_rows_kernel<T>, dim3((unsigned)rows), dim3(256), 0, stream, x, delta, idx, out, size);
 }
 
+// ---------------------------------------------------------------- rows of a checkpoint tensor into their place (load time)
+// dst row = dst_row0 + (r / block_rows) * dst_block_stride + r % block_rows for source row r, converted from S to
+// D on the way (bfloat16 -> float32 exactly, float32 -> bfloat16 by rounding).  With block_rows = the row count it
+// is a copy of consecutive rows (the q, k and v matrices into one); with block_rows 8 and a stride of 16 it
+// interleaves the gate rows (dst_row0 0) and the up rows (dst_row0 8) of a feed-forward in blocks of eight.
+template <typename S, typename D>
+__global__ void place_rows_kernel(const S* __restrict__ src, D* __restrict__ dst, int64_t rows, int64_t cols,
+                                  int64_t block_rows, int64_t dst_block_stride, int64_t dst_row0) {
+    const int64_t total = rows * cols;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / cols, c = i % cols;
+        const int64_t to = dst_row0 + (r / block_rows) * dst_block_stride + r % block_rows;
+        dst[to * cols + c] = from_f32<D>(to_f32<S>(src[i]));
+    }
+}
+
+template <typename S, typename D>
+static int place_rows_launch(const void* src, void* dst, int64_t rows, int64_t cols, int64_t block_rows,
+                             int64_t dst_block_stride, int64_t dst_row0, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (block_rows <= 0 || dst_block_stride < block_rows || dst_row0 < 0) return Q3_ERR_BAD_SIZE;
+    const int threads = 256;
+    int64_t blocks = (rows * cols + threads - 1) / threads;
+    const int64_t resident = (int64_t)q3_device_sm_count() * 8;
+    if (blocks > resident) blocks = resident;
+    return (int)q3_launch(place_rows_kernel<S, D>, dim3((unsigned)blocks), dim3(threads), 0, stream, (const S*)src, (D*)dst, rows,
+                          cols, block_rows, dst_block_stride, dst_row0);
+}
+
+// src_kind / dst_kind: 0 = float32, 1 = bfloat16.
+Q3_EXPORT int q3_place_rows(const void* src, int src_kind, void* dst, int dst_kind, int64_t rows, int64_t cols,
+                            int64_t block_rows, int64_t dst_block_stride, int64_t dst_row0, void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (src_kind == 0 && dst_kind == 0) return place_rows_launch<float, float>(src, dst, rows, cols, block_rows, dst_block_stride, dst_row0, s);
+    if (src_kind == 0 && dst_kind == 1) return place_rows_launch<float, bf16>(src, dst, rows, cols, block_rows, dst_block_stride, dst_row0, s);
+    if (src_kind == 1 && dst_kind == 0) return place_rows_launch<bf16, float>(src, dst, rows, cols, block_rows, dst_block_stride, dst_row0, s);
+    if (src_kind == 1 && dst_kind == 1) return place_rows_launch<bf16, bf16>(src, dst, rows, cols, block_rows, dst_block_stride, dst_row0, s);
+    return Q3_ERR_BAD_SIZE;
+}
+
 // ---------------------------------------------------------------- exported entry points
 #define Q3_ELEMENTWISE_EXPORTS(SUFFIX, T)                                                                          \
     Q3_EXPORT int q3_embedding_##SUFFIX(const int* ids, const void* table, void* out, int64_t n_tokens, int hidden, \

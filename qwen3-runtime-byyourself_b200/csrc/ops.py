@@ -241,6 +241,27 @@ def gather_rows(x: torch.Tensor, idx: torch.Tensor, out: torch.Tensor, delta: Op
     return out
 
 
+def place_rows(src: torch.Tensor, dst: torch.Tensor, block_rows: int = 0, dst_block_stride: int = 0, dst_row0: int = 0):
+    """Rows of `src` [rows, cols] into `dst` [*, cols], converted to dst's type on the way: source row r goes to
+    row dst_row0 + (r // block_rows) * dst_block_stride + r % block_rows (block_rows 0: one block, consecutive
+    rows from dst_row0).  Load time: the q, k and v matrices into one, gate and up rows interleaved."""
+    kinds = {torch.float32: 0, torch.bfloat16: 1}
+    if src.dtype not in kinds or dst.dtype not in kinds:
+        raise KernelError("place_rows: float32 or bfloat16 on either side")
+    rows, cols = src.shape
+    block = int(block_rows) or rows
+    stride = int(dst_block_stride) or block
+    if dst.shape[-1] != cols or rows % block != 0:
+        raise KernelError("place_rows: shapes do not fit")
+    last = dst_row0 + (rows // block - 1) * stride + block if rows else 0
+    if last > dst.shape[0]:
+        raise KernelError("place_rows: the rows do not fit the destination")
+    fn = _fn("elementwise.cu", "q3_place_rows", [c_void_p, c_int, c_void_p, c_int] + [c_int64] * 5 + [c_void_p])
+    _check(fn(_dev(src, "src"), kinds[src.dtype], _dev(dst, "dst"), kinds[dst.dtype], rows, cols, block, stride, int(dst_row0),
+              _stream()), "place_rows")
+    return dst
+
+
 # ------------------------------------------------------------------ matrix products
 def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[M, N] = x[M, K] . w[N, K]^T in true 32-bit (fmaf, fixed order over K)."""

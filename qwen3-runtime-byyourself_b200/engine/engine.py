@@ -26,7 +26,7 @@ from ..cache.storage import KVCache
 from ..config.registry import load_config
 from ..csrc.build import KernelBuildError
 from ..parts.model import Model, build_model
-from ..weights.loader import load_weights, random_weights
+from ..weights.loader import open_upload, random_weights
 from .context import Scratch, StepContext
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -266,10 +266,14 @@ class Engine:
         """Load config.json and the safetensors of `folder`; the model class is chosen by config.json."""
         config = load_config(folder)
         model = build_model(config.plan())
-        weights = load_weights(folder, model.weight_specs(), model.ignorable_names())
         compute = DTYPES[dtype] if dtype is not None else DTYPES[getattr(config, "torch_dtype", "bfloat16")]
-        model.bind(weights, compute, device)
-        return cls(model, config, max_tokens, max_seq_len, n_slots, use_graphs)
+        # every tensor goes from the mapped file to its final place on the device in one pass
+        source = open_upload(folder, model.weight_specs(), model.ignorable_names(), compute, device, model._warn_rounding)
+        model.bind(source, compute, device)
+        source.finish()
+        engine = cls(model, config, max_tokens, max_seq_len, n_slots, use_graphs)
+        engine.weights_arena = source.arena                    # the parts' tensors are views of it
+        return engine
 
     @classmethod
     def from_random(cls, config, seed: int, dtype=None, max_tokens: int = 4096, max_seq_len: Optional[int] = None,

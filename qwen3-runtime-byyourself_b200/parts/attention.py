@@ -18,6 +18,7 @@ from ..cache.book import CacheNeed
 from ..config.plan import PartSpec
 from ..csrc import ops
 from ..weights.loader import WeightSpec
+from ..weights.upload import fuse_rows
 from .base import Part, build_part, register_part
 from .linear import linear
 
@@ -57,8 +58,7 @@ class GQAAttention(Part):
 
     def bind(self, weights: dict, prefix: str, dtype, device) -> None:
         p = prefix + self.prefix
-        self.w_qkv = torch.cat([weights.pop(p + "q_proj.weight"), weights.pop(p + "k_proj.weight"),
-                                weights.pop(p + "v_proj.weight")], dim=0).contiguous()
+        self.w_qkv = fuse_rows(weights, [p + "q_proj.weight", p + "k_proj.weight", p + "v_proj.weight"])
         self.w_o = weights.pop(p + "o_proj.weight").contiguous()
         if self.q_norm is not None:
             self.q_norm.bind(weights, p + "q_norm.weight", dtype, device)

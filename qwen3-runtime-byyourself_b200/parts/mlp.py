@@ -11,6 +11,7 @@ import torch
 
 from ..csrc import ops
 from ..weights.loader import WeightSpec
+from ..weights.upload import fuse_interleaved, fuse_rows
 from .base import Part, register_part
 from . import linear as linear_module
 from .linear import linear
@@ -28,11 +29,11 @@ class SwiGLU(Part):
 
     def bind(self, weights: dict, prefix: str, dtype, device) -> None:
         p = prefix + self.prefix
-        gate, up = weights.pop(p + "gate_proj.weight"), weights.pop(p + "up_proj.weight")
+        gate, up = p + "gate_proj.weight", p + "up_proj.weight"
         # gate and up rows interleaved in blocks of eight: one product gives both, and a kernel that owns
         # 16 consecutive output rows can finish silu(g) * u itself
         self.interleaved = self.intermediate_size % 8 == 0
-        self.w_gate_up = ops.interleave_gate_up(gate, up) if self.interleaved else torch.cat([gate, up], dim=0).contiguous()
+        self.w_gate_up = fuse_interleaved(weights, gate, up, 8) if self.interleaved else fuse_rows(weights, [gate, up])
         self.w_down = weights.pop(p + "down_proj.weight").contiguous()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:

@@ -49,32 +49,29 @@ class Model:
     def ignorable_names(self) -> List[str]:
         return list(getattr(self.head, "ignorable", lambda prefix: [])(self.plan.head_prefix))
 
-    def bind(self, weights: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
-        """Take the tensors (by checkpoint name) for computing in `dtype` on `device`.
+    def bind(self, weights, dtype: torch.dtype, device) -> None:
+        """Take the tensors (by checkpoint name) for computing in `dtype` on `device`.  `weights` is a dict of
+        tensors, or a checkpoint that uploads on demand (`weights.loader.open_upload`).
 
         Matrices are used in the compute type: a bfloat16 checkpoint widens exactly for
         the 32-bit path; a 32-bit matrix is rounded to bfloat16 for a bfloat16 engine, with
         one line on stderr saying so.  Scale vectors are always read as float32."""
-        specs = self.weight_specs()
-        prepared = {}
-        for name, spec in specs.items():
-            t = weights[name]
-            if spec.role == "matrix":
-                if t.dtype == torch.float32 and dtype == torch.bfloat16 and not self._warned_rounding:
-                    self._warned_rounding = True
-                    print(f"[qwen3_b200] {name} (and other matrices) are stored in 32-bit and are rounded to bfloat16 "
-                          f"for the bfloat16 kernels; use dtype float32 to compute with them as stored", file=sys.stderr)
-                t = t.to(device=device, dtype=dtype)
-            else:
-                t = t.to(device=device)
-            prepared[name] = t
+        from ..weights.upload import TensorDict
+        if isinstance(weights, dict):
+            weights = TensorDict(weights, self.weight_specs(), dtype, device, self._warn_rounding)
         p = self.plan
         self.dtype, self.device = dtype, torch.device(device)
-        self.embedding.bind(prepared, p.embedding_prefix, dtype, device)
-        self.final_norm.bind(prepared, p.final_norm_prefix + "weight", dtype, device)
-        self.head.bind(prepared, p.head_prefix, dtype, device)
+        self.embedding.bind(weights, p.embedding_prefix, dtype, device)
+        self.final_norm.bind(weights, p.final_norm_prefix + "weight", dtype, device)
+        self.head.bind(weights, p.head_prefix, dtype, device)
         for spec, block in zip(p.layers, self.blocks):
-            block.bind(prepared, spec.prefix, dtype, device)
+            block.bind(weights, spec.prefix, dtype, device)
+
+    def _warn_rounding(self, name: str) -> None:
+        if not self._warned_rounding:
+            self._warned_rounding = True
+            print(f"[qwen3_b200] {name} (and other matrices) are stored in 32-bit and are rounded to bfloat16 "
+                  f"for the bfloat16 kernels; use dtype float32 to compute with them as stored", file=sys.stderr)
 
     # -- cache
     def cache_needs(self) -> List[Optional[CacheNeed]]:

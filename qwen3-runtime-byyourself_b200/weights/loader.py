@@ -60,10 +60,9 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
-def load_weights(folder: str, specs: Dict[str, WeightSpec], ignorable: Iterable[str] = (),
-                 device: str = "cpu") -> Dict[str, torch.Tensor]:
-    """Read the tensors named by `specs` from `folder`, in their stored dtypes, onto `device`."""
-    ckpt = Checkpoint(folder)
+def check_checkpoint(ckpt: Checkpoint, folder: str, specs: Dict[str, WeightSpec], ignorable: Iterable[str] = ()) -> None:
+    """Raise the one `WeightError` that lists everything in which the checkpoint and the model's own list of
+    tensors differ; nothing is read beyond the headers."""
     have = set(ckpt.names())
     missing = [n for n in specs if n not in have]
     unexpected = [n for n in have if n not in specs and n not in set(ignorable)]
@@ -79,11 +78,28 @@ def load_weights(folder: str, specs: Dict[str, WeightSpec], ignorable: Iterable[
             wrong_dtype.append((name, str(info.dtype), spec.role))
     if missing or unexpected or wrong_shape or wrong_dtype:
         raise WeightError(folder, missing, unexpected, wrong_shape, wrong_dtype)
+
+
+def load_weights(folder: str, specs: Dict[str, WeightSpec], ignorable: Iterable[str] = (),
+                 device: str = "cpu") -> Dict[str, torch.Tensor]:
+    """Read the tensors named by `specs` from `folder`, in their stored dtypes, onto `device` (each as a tensor
+    of its own; a model that is bound for a device goes through `open_upload` instead)."""
+    ckpt = Checkpoint(folder)
+    check_checkpoint(ckpt, folder, specs, ignorable)
     out = {}
     for name in specs:
         t = ckpt.tensor(name)
         out[name] = t.to(device, non_blocking=False) if device != "cpu" else t.clone()
     return out
+
+
+def open_upload(folder: str, specs: Dict[str, WeightSpec], ignorable: Iterable[str], dtype: torch.dtype, device, warn=None):
+    """The checkpoint of `folder`, checked against `specs`, as a source that a model binds from: every tensor goes
+    from the mapped file to its final place on the device in one pass (weights/upload.py)."""
+    from .upload import CheckpointUpload
+    ckpt = Checkpoint(folder)
+    check_checkpoint(ckpt, folder, specs, ignorable)
+    return CheckpointUpload(ckpt, specs, dtype, device, warn)
 
 
 def _stream_seed(seed: int, name: str) -> int:
