@@ -1,4 +1,5 @@
-"""Bookkeeping of the cache on the host: slots, lengths, pages, groups.  No tensors.
+"""Bookkeeping of the cache on the host: slots, lengths, pages, groups.  No tensors.  The book is a C++ class
+(include/qwen3/cache_book.h) behind a C face (csrc/host_runtime.cpp); this module is its binding.
 
 A *slot* belongs to one sequence from its first step until the batch gives it
 back.  Keys and values live in *pages* of `PAGE_TOKENS` tokens; a slot holds, for
@@ -15,6 +16,7 @@ are kept here per slot, and `reset` is logical only as there (:206-214).
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -57,92 +59,85 @@ class CacheFull(CacheError):
     """No slot or not enough pages are free for what was asked."""
 
 
-class SlotAllocator:
-    """Hands out slot numbers; a slot is held once and freed once."""
+def _host():
+    """The host runtime (include/qwen3/cache_book.h, step_pack.h behind csrc/host_runtime.cpp), loaded once."""
+    global _lib
+    if _lib is None:
+        from ..csrc.build import load_library
+        lib = load_library("host_runtime.cpp")
+        i32p, i64p = ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int64)
+        lib.q3_host_last_error.restype = ctypes.c_char_p
+        lib.q3_book_create.argtypes = [i32p, i32p, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int,
+                                       ctypes.POINTER(ctypes.c_void_p)]
+        lib.q3_book_destroy.argtypes = [ctypes.c_void_p]
+        lib.q3_book_destroy.restype = None
+        lib.q3_book_info.argtypes = [ctypes.c_void_p, i32p]
+        lib.q3_book_info.restype = ctypes.c_int64
+        lib.q3_book_alloc_slot.argtypes = [ctypes.c_void_p, i32p]
+        lib.q3_book_free_slot.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        for name in ("q3_book_reserve", "q3_book_commit", "q3_book_cancel"):
+            getattr(lib, name).argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
+        lib.q3_book_lengths.argtypes = [ctypes.c_void_p]
+        lib.q3_book_lengths.restype = i64p
+        lib.q3_book_is_held.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        lib.q3_book_free_slots.argtypes = [ctypes.c_void_p]
+        lib.q3_book_pages_held.argtypes = [ctypes.c_void_p]
+        lib.q3_book_table.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        lib.q3_book_table.restype = i32p
+        lib.q3_book_free_pages.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        lib.q3_step_layout.argtypes = [ctypes.c_int] * 5 + [ctypes.c_void_p]
+        lib.q3_pack_step.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64,
+                                     ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        lib.q3_pack_decode_step.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+                                            ctypes.c_void_p]
+        _lib = lib
+    return _lib
 
-    def __init__(self, n_slots: int):
-        self.n_slots = n_slots
-        self._free = list(range(n_slots - 1, -1, -1))
-        self._held = set()
 
-    def alloc(self) -> int:
-        if not self._free:
-            raise CacheFull(f"all {self.n_slots} slots are held")
-        slot = self._free.pop()
-        self._held.add(slot)
-        return slot
+_lib = None
 
-    def free(self, slot: int) -> None:
-        if slot not in self._held:
-            raise CacheError(f"slot {slot} is not held (freed twice, or never handed out)")
-        self._held.remove(slot)
-        self._free.append(slot)
+
+def _raise(code: int) -> None:
+    message = _host().q3_host_last_error().decode("utf-8", "replace")
+    raise {1: CacheError, 2: CacheFull}.get(code, RuntimeError)(message)
+
+
+class _Slots:
+    """The slots of a book: which are held, how many are free."""
+
+    def __init__(self, book: "CacheBook"):
+        self._book = book
 
     def is_held(self, slot: int) -> bool:
-        return slot in self._held
+        return bool(_host().q3_book_is_held(self._book._handle, int(slot)))
 
     @property
     def n_free(self) -> int:
-        return len(self._free)
+        return int(_host().q3_book_free_slots(self._book._handle))
 
     @property
     def held(self):
-        return frozenset(self._held)
+        return frozenset(s for s in range(self._book.n_slots) if self.is_held(s))
 
 
 class PageGroup:
-    """The pages of the layers that share one `CacheNeed`."""
+    """The pages of the layers that share one `CacheNeed`: a view of the book's group."""
 
-    def __init__(self, need: CacheNeed, layers: List[int], n_pages: int, n_slots: int, pages_per_slot: int):
-        self.need, self.layers, self.n_pages = need, layers, n_pages
-        self._free = list(range(n_pages - 1, -1, -1))
-        self.table = np.full((n_slots, pages_per_slot), -1, dtype=np.int32)
-        self.first_live = np.zeros(n_slots, dtype=np.int64)   # first page index still held (window groups)
+    def __init__(self, book: "CacheBook", index: int, need: CacheNeed, layers: List[int]):
+        self._book, self._index, self.need, self.layers = book, index, need, layers
+        self.n_pages = book.n_pages
+        pointer = _host().q3_book_table(book._handle, index)
+        self.table = np.ctypeslib.as_array(pointer, shape=(book.n_slots, book.pages_per_slot))   # -1: no page
+
+    @property
+    def _free(self) -> List[int]:
+        out = np.empty(self.n_pages, dtype=np.int32)
+        n = _host().q3_book_free_pages(self._book._handle, self._index, out.ctypes.data)
+        return [int(p) for p in out[:n]]
 
     @property
     def n_free(self) -> int:
-        return len(self._free)
-
-    def pages_needed(self, length_now: int, n_new: int) -> int:
-        have = -(-length_now // PAGE_TOKENS)
-        want = -(-(length_now + n_new) // PAGE_TOKENS)
-        return want - have
-
-    def extend(self, slot: int, length_now: int, n_new: int) -> None:
-        have = -(-length_now // PAGE_TOKENS)
-        want = -(-(length_now + n_new) // PAGE_TOKENS)
-        for i in range(have, want):
-            self.table[slot, i] = self._free.pop()
-
-    def shrink(self, slot: int, length_now: int, n_new: int) -> None:
-        """Undo `extend(slot, length_now, n_new)`: the pages it took go back to the pool."""
-        have = -(-length_now // PAGE_TOKENS)
-        want = -(-(length_now + n_new) // PAGE_TOKENS)
-        for i in range(want - 1, have - 1, -1):
-            page = int(self.table[slot, i])
-            if page >= 0:
-                self._free.append(page)
-                self.table[slot, i] = -1
-
-    def trim_window(self, slot: int, length: int) -> None:
-        """Give back the pages that no later query of this sequence can read."""
-        if self.need.kind != "window":
-            return
-        # a query at position >= length reads keys > length - window
-        dead_pages = max(0, (length - self.need.window + 1) // PAGE_TOKENS)
-        for i in range(int(self.first_live[slot]), dead_pages):
-            page = int(self.table[slot, i])
-            if page >= 0:
-                self._free.append(page)
-                self.table[slot, i] = -1
-        self.first_live[slot] = max(int(self.first_live[slot]), dead_pages)
-
-    def release(self, slot: int) -> None:
-        row = self.table[slot]
-        for page in row[row >= 0]:
-            self._free.append(int(page))
-        row[:] = -1
-        self.first_live[slot] = 0
+        return int(_host().q3_book_free_pages(self._book._handle, self._index, None))
 
     def held_pages(self, slot: int) -> List[int]:
         row = self.table[slot]
@@ -150,7 +145,8 @@ class PageGroup:
 
 
 class CacheBook:
-    """Slots, lengths and pages of every group; the storage class adds the tensors.
+    """Slots, lengths and pages of every group; the storage class adds the tensors.  The book itself is the
+    C++ class of include/qwen3/cache_book.h; this is its binding.
 
     `needs[i]` is the need of layer i, or None for a layer that reads another
     layer's cache.  `max_tokens` is the most tokens that live sequences hold at
@@ -163,16 +159,11 @@ class CacheBook:
         if max_tokens <= 0 or max_seq_len <= 0:
             raise ValueError("max_tokens and max_seq_len must be positive")
         self.page_tokens = PAGE_TOKENS
-        self.n_pages = -(-max_tokens // PAGE_TOKENS)
-        self.max_seq_len = min(max_seq_len, self.n_pages * PAGE_TOKENS)
-        self.pages_per_slot = -(-self.max_seq_len // PAGE_TOKENS)
-        self.n_slots = n_slots if n_slots is not None else self.n_pages
-        self.slots = SlotAllocator(self.n_slots)
-        self.lengths = np.zeros(self.n_slots, dtype=np.int64)
-        self.groups: List[PageGroup] = []
         self.group_of_layer: Dict[int, int] = {}
         self.state_layers: Dict[int, Tuple[int, ...]] = {}
         by_key: Dict[tuple, int] = {}
+        group_needs: List[CacheNeed] = []
+        group_layers: List[List[int]] = []
         for layer, need in enumerate(needs):
             if need is None:
                 continue
@@ -182,23 +173,46 @@ class CacheBook:
                 continue
             key = need.group_key()
             if key not in by_key:
-                by_key[key] = len(self.groups)
-                self.groups.append(PageGroup(need, [], self.n_pages, self.n_slots, self.pages_per_slot))
-            self.groups[by_key[key]].layers.append(layer)
+                by_key[key] = len(group_needs)
+                group_needs.append(need)
+                group_layers.append([])
+            group_layers[by_key[key]].append(layer)
             self.group_of_layer[layer] = by_key[key]
+        G = len(group_needs)
+        kinds = (ctypes.c_int32 * max(G, 1))(*[1 if n.kind == "window" else 0 for n in group_needs])
+        windows = (ctypes.c_int32 * max(G, 1))(*[int(n.window or 0) for n in group_needs])
+        handle = ctypes.c_void_p()
+        code = _host().q3_book_create(kinds, windows, G, int(max_tokens), int(max_seq_len), int(n_slots or 0), PAGE_TOKENS,
+                                      ctypes.byref(handle))
+        if code:
+            _raise(code)
+        self._handle = handle
+        info = (ctypes.c_int32 * 5)()
+        self.max_seq_len = int(_host().q3_book_info(self._handle, info))
+        self.n_pages, self.n_slots, self.pages_per_slot = int(info[0]), int(info[1]), int(info[2])
+        self.lengths = np.ctypeslib.as_array(_host().q3_book_lengths(self._handle), shape=(self.n_slots,))
+        self.slots = _Slots(self)
+        self.groups: List[PageGroup] = [PageGroup(self, g, group_needs[g], group_layers[g]) for g in range(G)]
+
+    def __del__(self):
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle and _lib is not None:
+            self.groups, self.lengths = [], None          # the views die with the book
+            _lib.q3_book_destroy(handle)
 
     # -- slots
     def alloc_slot(self) -> int:
-        slot = self.slots.alloc()
-        self.lengths[slot] = 0
-        self._on_alloc(slot)
-        return slot
+        slot = ctypes.c_int32()
+        code = _host().q3_book_alloc_slot(self._handle, ctypes.byref(slot))
+        if code:
+            _raise(code)
+        self._on_alloc(slot.value)
+        return int(slot.value)
 
     def free_slot(self, slot: int) -> None:
-        self.slots.free(slot)
-        for g in self.groups:
-            g.release(slot)
-        self.lengths[slot] = 0
+        code = _host().q3_book_free_slot(self._handle, int(slot))
+        if code:
+            _raise(code)
 
     def length(self, slot: int) -> int:
         return int(self.lengths[slot])
@@ -206,43 +220,34 @@ class CacheBook:
     def _on_alloc(self, slot: int) -> None:  # the storage class zeroes the state rows here
         pass
 
-    # -- a step: reserve for every sequence, run, commit
+    # -- a step: reserve for every sequence, run, commit (or cancel)
+    @staticmethod
+    def _arrays(step: Sequence[Tuple[int, int]]):
+        slots = np.fromiter((s for s, _ in step), dtype=np.int32, count=len(step))
+        n_new = np.fromiter((n for _, n in step), dtype=np.int64, count=len(step))
+        return slots, n_new
+
     def reserve(self, step: Sequence[Tuple[int, int]]) -> None:
         """Make room for `n_new` tokens on each `(slot, n_new)`; nothing changes if it cannot be done."""
-        seen = set()
-        for slot, n_new in step:
-            if not self.slots.is_held(slot):
-                raise CacheError(f"slot {slot} is not held")
-            if slot in seen:
-                raise CacheError(f"slot {slot} appears twice in one step")
-            seen.add(slot)
-            if n_new <= 0:
-                raise CacheError(f"slot {slot}: a step needs at least one token")
-            if self.lengths[slot] + n_new > self.max_seq_len:
-                raise CacheFull(f"slot {slot}: {int(self.lengths[slot])} + {n_new} tokens exceed the "
-                                f"sequence capacity {self.max_seq_len}")
-        for g in self.groups:
-            need = sum(g.pages_needed(int(self.lengths[s]), n) for s, n in step)
-            if need > g.n_free:
-                raise CacheFull(f"the step needs {need} pages of {PAGE_TOKENS} tokens, {g.n_free} are free "
-                                f"(of {g.n_pages})")
-        for g in self.groups:
-            for slot, n_new in step:
-                g.extend(slot, int(self.lengths[slot]), n_new)
+        slots, n_new = self._arrays(step)
+        code = _host().q3_book_reserve(self._handle, slots.ctypes.data, n_new.ctypes.data, len(step))
+        if code:
+            _raise(code)
 
     def cancel(self, step: Sequence[Tuple[int, int]]) -> None:
         """The step did not run after all (its launch failed): the pages that `reserve` took for it go back,
         lengths stay as they were.  What the failed step may have written lies beyond every length."""
-        for g in self.groups:
-            for slot, n_new in step:
-                g.shrink(slot, int(self.lengths[slot]), n_new)
+        slots, n_new = self._arrays(step)
+        code = _host().q3_book_cancel(self._handle, slots.ctypes.data, n_new.ctypes.data, len(step))
+        if code:
+            _raise(code)
 
     def commit(self, step: Sequence[Tuple[int, int]]) -> None:
         """The step ran: lengths advance once, window groups return dead pages."""
-        for slot, n_new in step:
-            self.lengths[slot] += n_new
-            for g in self.groups:
-                g.trim_window(slot, int(self.lengths[slot]))
+        slots, n_new = self._arrays(step)
+        code = _host().q3_book_commit(self._handle, slots.ctypes.data, n_new.ctypes.data, len(step))
+        if code:
+            _raise(code)
 
     # -- views for a step
     def page_rows(self, group: int, slots: Sequence[int]) -> np.ndarray:
@@ -251,4 +256,27 @@ class CacheBook:
 
     def pages_held(self) -> int:
         """Pages in use in the fullest group: what counts against `max_tokens`."""
-        return max((g.n_pages - g.n_free for g in self.groups), default=0)
+        return int(_host().q3_book_pages_held(self._handle))
+
+    # -- the metadata of a step, packed by the host runtime (include/qwen3/step_pack.h)
+    def step_layout(self, n_tokens: int, n_seqs: int, n_want: int) -> Tuple[List[int], int]:
+        """Offsets of the sections token_ids, token_seq, token_pos, seq_slots, seq_start, seq_pos0, want_rows and of
+        one page table per group in a step's int32 buffer, and the buffer's size."""
+        G = len(self.groups)
+        offsets = (ctypes.c_int32 * (7 + G))()
+        total = _host().q3_step_layout(int(n_tokens), int(n_seqs), int(n_want), G, self.pages_per_slot, offsets)
+        return [int(o) for o in offsets], int(total)
+
+    def pack_step(self, slots: np.ndarray, n_new: np.ndarray, token_ids: np.ndarray, want_rows: np.ndarray, out: np.ndarray) -> None:
+        """Fill `out` (int32, the size `step_layout` gives) for the step; `reserve` has run, `commit` has not."""
+        code = _host().q3_pack_step(self._handle, slots.ctypes.data, n_new.ctypes.data, len(slots), token_ids.ctypes.data,
+                                    int(token_ids.size), want_rows.ctypes.data, int(want_rows.size), out.ctypes.data)
+        if code:
+            _raise(code)
+
+    def pack_decode_step(self, rows: int, slots: np.ndarray, token_ids: np.ndarray, out: np.ndarray) -> None:
+        """The same for a decode step of a fixed number of `rows`, the rows beyond len(slots) being padding."""
+        code = _host().q3_pack_decode_step(self._handle, int(rows), slots.ctypes.data, len(slots), token_ids.ctypes.data,
+                                           out.ctypes.data)
+        if code:
+            _raise(code)

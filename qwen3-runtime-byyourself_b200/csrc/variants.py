@@ -4,6 +4,7 @@ head sizes of the shipped configurations; `build()` of the build driver compiles
 
 def all_variants():
     return [
+        ("host_runtime.cpp", ()),
         ("elementwise.cu", ()),
         ("gemm_f32.cu", ()),
         ("attention.cu", ()),

@@ -46,26 +46,15 @@ class StepError(ValueError):
     """A step that cannot run: empty, out-of-vocabulary ids, a wanted place outside the tokens."""
 
 
-def _align4(n: int) -> int:
-    return (n + 3) & ~3
-
-
 class _MetaLayout:
-    """Offsets of the sections of the step's int32 metadata buffer."""
+    """Offsets of the sections of the step's int32 metadata buffer, as the host runtime lays them out
+    (include/qwen3/step_pack.h)."""
 
-    def __init__(self, n_tokens: int, n_seqs: int, n_want: int, n_groups: int, pages_per_slot: int):
-        o = 0
-        self.token_ids = o; o += _align4(n_tokens)
-        self.token_seq = o; o += _align4(n_tokens)
-        self.token_pos = o; o += _align4(n_tokens)
-        self.seq_slots = o; o += _align4(n_seqs)
-        self.seq_start = o; o += _align4(n_seqs + 1)
-        self.seq_pos0 = o; o += _align4(n_seqs)
-        self.want_rows = o; o += _align4(max(n_want, 1))
-        self.tables = []
-        for _ in range(n_groups):
-            self.tables.append(o); o += _align4(n_seqs * pages_per_slot)
-        self.total = o
+    def __init__(self, cache, n_tokens: int, n_seqs: int, n_want: int):
+        offsets, self.total = cache.step_layout(n_tokens, n_seqs, n_want)
+        (self.token_ids, self.token_seq, self.token_pos, self.seq_slots, self.seq_start, self.seq_pos0,
+         self.want_rows) = offsets[:7]
+        self.tables = offsets[7:]
 
 
 class _MetaBuffer:
@@ -120,30 +109,19 @@ def context_views(cache, dev, lay, N, B, R, scratch, dtype, max_positions, is_de
 
 def build_context(cache, meta: "_MetaBuffer", scratch, dtype, max_positions, slots, n_new, pos0, token_ids,
                   want_rows) -> StepContext:
-    """Pack one step's metadata, upload it with one copy and return the context the parts read.
-    `cache.reserve` must have made room for the step already (the page rows are read here)."""
-    token_ids = np.asarray(token_ids, dtype=np.int64).reshape(-1)
+    """Pack one step's metadata (the host runtime does it, in C++), upload it with one copy and return the context
+    the parts read.  `cache.reserve` must have made room for the step already (the page rows are read here)."""
+    token_ids = np.ascontiguousarray(token_ids, dtype=np.int32).reshape(-1)
     B, N, R = len(slots), int(token_ids.size), len(want_rows)
-    G, P = len(cache.groups), cache.pages_per_slot
-    lay = _MetaLayout(N, B, R, G, P)
+    lay = _MetaLayout(cache, N, B, R)
     host = meta.stage(lay.total)
-    n_new_a, pos0_a = np.asarray(n_new, dtype=np.int64), np.asarray(pos0, dtype=np.int64)
-    seq_start = np.zeros(B + 1, dtype=np.int64)
-    np.cumsum(n_new_a, out=seq_start[1:])
-    token_seq = np.repeat(np.arange(B, dtype=np.int64), n_new_a)
-    token_pos = np.arange(N, dtype=np.int64) - seq_start[:-1][token_seq] + pos0_a[token_seq]
-    host[lay.token_ids:lay.token_ids + N] = token_ids
-    host[lay.token_seq:lay.token_seq + N] = token_seq
-    host[lay.token_pos:lay.token_pos + N] = token_pos
-    host[lay.seq_slots:lay.seq_slots + B] = slots
-    host[lay.seq_start:lay.seq_start + B + 1] = seq_start
-    host[lay.seq_pos0:lay.seq_pos0 + B] = pos0_a
-    host[lay.want_rows:lay.want_rows + R] = want_rows
-    for g in range(G):
-        host[lay.tables[g]:lay.tables[g] + B * P] = cache.page_rows(g, slots).reshape(-1)
+    slots_a = np.asarray(slots, dtype=np.int32)
+    n_new_a = np.asarray(n_new, dtype=np.int64)
+    cache.pack_step(slots_a, n_new_a, token_ids, np.asarray(want_rows, dtype=np.int32), host)
     meta.upload(lay.total)
-    return context_views(cache, meta.dev, lay, N, B, R, scratch, dtype, max_positions, bool(n_new_a.max() == 1),
-                         int(n_new_a.max()), int((pos0_a + n_new_a).max()), host=(slots, n_new, pos0),
+    longest = int(n_new_a.max())
+    return context_views(cache, meta.dev, lay, N, B, R, scratch, dtype, max_positions, longest == 1, longest,
+                         int((np.asarray(pos0, dtype=np.int64) + n_new_a).max()), host=(slots, n_new, pos0),
                          want_all=(R == N and list(want_rows) == list(range(N))))
 
 
@@ -165,8 +143,7 @@ class _DecodeGraph:
     def __init__(self, engine: "Engine", rows: int):
         self.engine, self.rows = weakref.proxy(engine), rows      # no cycle: an engine dies with its last reference
         cache = engine.cache
-        G, P = len(cache.groups), cache.pages_per_slot
-        self.layout = _MetaLayout(rows, rows, rows, G, P)
+        self.layout = _MetaLayout(cache, rows, rows, rows)
         self.meta = _MetaBuffer(engine.device)
         self.meta.reserve(self.layout.total)
         self.scratch = Scratch(engine.device)
@@ -178,23 +155,10 @@ class _DecodeGraph:
         self.launches = 0
 
     def _fill(self, slots, pos0, token_ids) -> None:
-        lay, rows, B = self.layout, self.rows, len(slots)
-        cache = self.engine.cache
+        lay = self.layout
         host = self.meta.stage(lay.total)
-        host[:] = 0
-        host[lay.token_ids:lay.token_ids + B] = token_ids
-        host[lay.token_seq:lay.token_seq + rows] = np.arange(rows)
-        host[lay.token_pos:lay.token_pos + B] = pos0
-        host[lay.seq_slots:lay.seq_slots + rows] = cache.n_slots      # the spare state row for padding
-        host[lay.seq_slots:lay.seq_slots + B] = slots
-        host[lay.seq_start:lay.seq_start + rows + 1] = np.arange(rows + 1)
-        host[lay.seq_pos0:lay.seq_pos0 + B] = pos0
-        host[lay.want_rows:lay.want_rows + rows] = np.arange(rows)
-        P = cache.pages_per_slot
-        for g in range(len(cache.groups)):
-            table = host[lay.tables[g]:lay.tables[g] + rows * P].reshape(rows, P)
-            table[:] = cache.n_pages                 # the spare page
-            table[:B] = cache.page_rows(g, slots)
+        self.engine.cache.pack_decode_step(self.rows, np.asarray(slots, dtype=np.int32),
+                                           np.ascontiguousarray(token_ids, dtype=np.int32).reshape(-1), host)
         self.meta.upload(lay.total)
 
     def _capture(self) -> None:

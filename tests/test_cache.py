@@ -3,23 +3,24 @@ sequence; groups with storage of their own; window groups return dead pages; sta
 import numpy as np
 import pytest
 
-from qwen3_b200.cache import PAGE_TOKENS, CacheBook, CacheError, CacheFull, CacheNeed, SlotAllocator
+from qwen3_b200.cache import PAGE_TOKENS, CacheBook, CacheError, CacheFull, CacheNeed
 
 FULL = CacheNeed("full", 2, 16)
 
 
-def test_slot_allocator_hands_out_each_slot_once_and_takes_it_back_once():
-    a = SlotAllocator(3)
-    got = [a.alloc(), a.alloc(), a.alloc()]
-    assert sorted(got) == [0, 1, 2] and a.n_free == 0
+def test_each_slot_is_handed_out_once_and_taken_back_once():
+    book = CacheBook([FULL], max_tokens=8 * PAGE_TOKENS, max_seq_len=PAGE_TOKENS, n_slots=3)
+    got = [book.alloc_slot(), book.alloc_slot(), book.alloc_slot()]
+    assert sorted(got) == [0, 1, 2] and book.slots.n_free == 0
     with pytest.raises(CacheFull):
-        a.alloc()
-    a.free(got[1])
+        book.alloc_slot()
+    book.free_slot(got[1])
     with pytest.raises(CacheError):
-        a.free(got[1])                       # freed twice
+        book.free_slot(got[1])               # freed twice
     with pytest.raises(CacheError):
-        a.free(7)                            # never handed out
-    assert a.alloc() == got[1] and a.held == frozenset(got)
+        book.free_slot(7)                    # never handed out
+    assert not book.slots.is_held(got[1]) and book.slots.is_held(got[0])
+    assert book.alloc_slot() == got[1] and book.slots.held == frozenset(got)
 
 
 def test_lengths_pages_and_reuse():
