@@ -93,6 +93,10 @@ class ClockSampler:
 
     def __init__(self, index=0):
         self.samples, self.proc, self.index = [], None, index
+        self.times, self.regions = [], []          # when each sample was read; (name, start, stop) of the timed regions
+
+    def region(self, name, start, stop):
+        self.regions.append((name, start, stop))
 
     def __enter__(self):
         try:
@@ -110,6 +114,7 @@ class ClockSampler:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) == 6:
                 self.samples.append(parts)
+                self.times.append(time.time())
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -125,9 +130,15 @@ class ClockSampler:
         mhz = [int(s[0]) for s in self.samples if s[0].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None,
-                "sm_max_mhz": int(self.samples[0][1]) if self.samples[0][1].isdigit() else None,
-                "reasons": reasons, "samples": len(self.samples)}
+        out = {"sm_mhz": int(statistics.median(mhz)) if mhz else None,
+               "sm_max_mhz": int(self.samples[0][1]) if self.samples[0][1].isdigit() else None,
+               "reasons": reasons, "samples": len(self.samples)}
+        # the same over the decode regions alone (the median above includes the prompt steps, which run at the power limit)
+        inside = [int(s[0]) for s, t in zip(self.samples, self.times)
+                  if s[0].isdigit() and any(a <= t <= b + 0.06 for name, a, b in self.regions if name == "decode")]
+        if inside:
+            out["sm_mhz_decode"], out["samples_decode"] = int(statistics.median(inside)), len(inside)
+        return out
 
 
 def unequal_lengths(n, longest, rng):
@@ -153,7 +164,7 @@ def prefill_flops(cfg, layers, T):
     return layers * (linear + attention) + 2 * V * H          # + the one row of logits that is wanted
 
 
-def decode_run(q, engine, sampler, torch, rng, batch, longest_prompt, steps, warmup):
+def decode_run(q, engine, sampler, torch, rng, batch, longest_prompt, steps, warmup, clocks=None):
     """Prefill `batch` unequal prompts in one step, then time `steps` decode steps on the device."""
     import numpy as np
     lengths = unequal_lengths(batch, longest_prompt, rng)
@@ -173,6 +184,7 @@ def decode_run(q, engine, sampler, torch, rng, batch, longest_prompt, steps, war
         logits = engine.step(entries, device_tokens=ids)
         ids.copy_(sampler.choose_device(logits, seq_ids, [step_index] * batch))
 
+    t_region = time.time()
     for i in range(warmup):
         one(1 + i)
     torch.cuda.synchronize()
@@ -183,6 +195,8 @@ def decode_run(q, engine, sampler, torch, rng, batch, longest_prompt, steps, war
         one(1 + warmup + i)
     stop.record()
     torch.cuda.synchronize()
+    if clocks is not None:
+        clocks.region("decode", t_region, time.time())
     ms = start.elapsed_time(stop) / steps
     cached = sum(engine.length(s) for s in slots) - batch * steps / 2.0      # mean over the timed steps
     launches = (engine.launches - launches_before) + steps                     # + the sampler's kernel
@@ -195,7 +209,7 @@ def decode_run(q, engine, sampler, torch, rng, batch, longest_prompt, steps, war
 E2E_SETTLE_STEPS = 40
 
 
-def e2e_run(q, engine, torch, rng, batch, longest_prompt, steps, warmup):
+def e2e_run(q, engine, torch, rng, batch, longest_prompt, steps, warmup, clocks=None):
     """Through `generate_token_ids`: host prompts in, host token ids out; the decode steps after
     the warm-up are timed on the host clock (each ends with the device-to-host read of its ids).
 
@@ -232,6 +246,8 @@ def e2e_run(q, engine, torch, rng, batch, longest_prompt, steps, warmup):
     torch.cuda.synchronize()
     # marks[k] is taken after step k's ids reached the host; step 0 is the prefill
     seconds = marks[warmup + steps] - marks[warmup]
+    if clocks is not None:                          # the decode steps after the prompt step settled
+        clocks.region("decode", time.time() - (time.perf_counter() - marks[E2E_SETTLE_STEPS // 2]), time.time())
     return {"tok_s": batch * steps / seconds, "ms": seconds / steps * 1e3, "warmup": warmup,
             "host_ms": busy[0] / max(busy[1], 1) * 1e3}
 
@@ -311,8 +327,11 @@ def main() -> int:
     torch.cuda.set_device(0)
     batch = args.batch or shape_batch
     max_batch = batch if (args.skip_points or args.shape != "8b") else max(batch, 64)
+    # the points at longer contexts (batch 8 at 2x and 4x the headline's) need longer sequences, not more pages
+    with_points = not args.skip_points and args.shape == "8b"
+    longest_context = 4 * CONTEXT if with_points else CONTEXT
     engine = q.Engine.from_random(config, seed=0, dtype="bfloat16", max_tokens=max_batch * CONTEXT,
-                                  max_seq_len=CONTEXT)
+                                  max_seq_len=longest_context)
     sampler = Sampler(q.SamplingParams(mode="greedy"), engine.vocab_size, engine.device)
 
     if args.kernels:
@@ -322,17 +341,24 @@ def main() -> int:
     # headline: batch 8 whose longest sequence ends at the context length
     clocks = ClockSampler()
     clocks.__enter__()                    # sampled through every arm, warm-up included
-    head = decode_run(q, engine, sampler, torch, rng, batch, CONTEXT - warmup - args.steps - 1, args.steps, warmup)
+    head = decode_run(q, engine, sampler, torch, rng, batch, CONTEXT - warmup - args.steps - 1, args.steps, warmup, clocks)
     step_bytes = weight_bytes_per_step(cfg, layers, batch) + head["cached_tokens"] * engine.cache.bytes_per_token()
     achieved = step_bytes / (head["ms"] * 1e-3) / 1e9
-    e2e = e2e_run(q, engine, torch, rng, batch, CONTEXT - warmup - E2E_SETTLE_STEPS - args.steps - 1, args.steps, warmup)
+    e2e = e2e_run(q, engine, torch, rng, batch, CONTEXT - warmup - E2E_SETTLE_STEPS - args.steps - 1, args.steps, warmup, clocks)
     h2d = engine.last_upload_bytes
 
     points = {}
     if not args.skip_points and args.shape == "8b":
         for b in (1, 64):
-            r = decode_run(q, engine, sampler, torch, rng, b, 2048, min(args.steps, 32), warmup)
+            r = decode_run(q, engine, sampler, torch, rng, b, 2048, min(args.steps, 32), warmup, clocks)
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
+        for factor in (2, 4):
+            ctx = factor * CONTEXT
+            r = decode_run(q, engine, sampler, torch, rng, batch, ctx - warmup - min(args.steps, 32) - 1, min(args.steps, 32), warmup,
+                           clocks)
+            points[f"decode_b{batch}_context{ctx}"] = round(r["tok_s"], 1)
+            moved = weight_bytes_per_step(cfg, layers, batch) + r["cached_tokens"] * engine.cache.bytes_per_token()
+            points[f"decode_b{batch}_context{ctx}_hbm_frac"] = round(moved / (r["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
 
     # prefill: one prompt of 2,048 tokens in one step
     times = []
