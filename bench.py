@@ -252,6 +252,56 @@ def e2e_run(q, engine, torch, rng, batch, longest_prompt, steps, warmup, clocks=
             "host_ms": busy[0] / max(busy[1], 1) * 1e3}
 
 
+def products_against_the_vendor_library(torch, cfg, copies=6, repeats=21):
+    """Microseconds of Y = X . W^T for the q/k/v, output, gate/up and down projections of one layer, per token
+    count: `ours` through parts.linear (the kernels the engine runs), `vendor` through torch.mm (cuBLAS).  Each
+    is a CUDA graph of `copies` products over different weights (more than the L2 holds), the median of
+    `repeats` replays divided by `copies`."""
+    from qwen3_b200.csrc import ops
+    from qwen3_b200.parts.linear import linear, tcgen05_form
+    H, I = cfg["hidden_size"], cfg["intermediate_size"]
+    d, nq, nkv = cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    shapes = [("qkv", (nq + 2 * nkv) * d, H), ("o", H, nq * d), ("gate_up", 2 * I, H), ("down", H, I)]
+
+    def replay_us(fn):
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(repeats):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        return statistics.median(times) / copies * 1e3
+
+    out = {"config": {"hidden": H, "intermediate": I, "copies": copies, "repeats": repeats}, "rows": []}
+    for M in (129, 256, 512, 1024, 2048, 4096):
+        sums = [0.0, 0.0]
+        for name, N, K in shapes:
+            ws = [torch.randn(N, K, device="cuda").to(torch.bfloat16) for _ in range(copies)]
+            x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+            y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            ours = replay_us(lambda: [linear(x, w, y) for w in ws])
+            vendor = replay_us(lambda: [torch.mm(x, w.t(), out=y) for w in ws])
+            out["rows"].append({"tokens": M, "product": name, "N": N, "K": K, "form": tcgen05_form(M, N, K),
+                                "ours_us": round(ours, 1), "vendor_us": round(vendor, 1), "ratio": round(ours / vendor, 3)})
+            sums[0] += ours
+            sums[1] += vendor
+            del ws
+        out["rows"].append({"tokens": M, "product": "all four", "ours_us": round(sums[0], 1), "vendor_us": round(sums[1], 1),
+                            "ratio": round(sums[0] / sums[1], 3)})
+    out["status_word"] = ops.tcgen05_status("cuda")
+    return out
+
+
 def kernel_breakdown(q, engine, sampler, torch, rng, batch, context, cfg, layers):
     """Microseconds per entry point of this library's kernels in one decode step of the headline batch and in
     one prompt step of 2,048 tokens, from CUDA events around every launch."""
@@ -298,6 +348,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=None, help="default: the shape's own (8b: 8, 14b: 16, 32b: 8)")
     ap.add_argument("--context", type=int, default=None, help="default: the shape's own (8b: 4096, 14b: 8192, 32b: 16384)")
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
+    ap.add_argument("--products", action="store_true",
+                    help="instead of the benchmark: the four projections of a layer at 129..4,096 tokens, this library's "
+                         "kernels against the vendor library's (torch.mm), both replayed from CUDA graphs over rotating weights")
     ap.add_argument("--kernels", action="store_true",
                     help="instead of the benchmark: time every kernel of one decode step and of one 2,048-token prompt step "
                          "with CUDA events (steps launched afresh, not replayed) and print the sums per entry point")
@@ -319,6 +372,10 @@ def main() -> int:
     from qwen3_b200.sampling.sampler import Sampler
 
     cfg, CONTEXT, shape_batch = SHAPES[args.shape]
+    if args.products:
+        torch.cuda.set_device(0)
+        print(json.dumps(products_against_the_vendor_library(torch, cfg)))
+        return 0
     CONTEXT = args.context or CONTEXT
     layers = args.layers or cfg["num_hidden_layers"]
     config = q.config_from_dict(dict(cfg, num_hidden_layers=layers))
