@@ -41,7 +41,7 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_
                                    const float* __restrict__ k_norm_w, const float* __restrict__ cos_tab,
                                    const float* __restrict__ sin_tab, const int* __restrict__ token_seq,
                                    const int* __restrict__ token_pos, const int* __restrict__ page_table,
-                                   int pages_per_seq, int nq, int nkv, int d, float eps, int write_kv) {
+                                   int pages_per_seq, int nq, int nkv, int d, float eps, int write_kv, int rot) {
     pdl_launch_dependents();
     pdl_wait();
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -49,7 +49,6 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_
     if (head >= nq + 2 * nkv || (head >= nq && !write_kv)) return;   // a layer that reads another layer's cache writes none
     const int64_t t = blockIdx.y;
     const int pos = token_pos[t];
-    const int half = d >> 1;
     const T* src = qkv + t * (int64_t)(nq + 2 * nkv) * d + (int64_t)head * d;
 
     T* dst;
@@ -67,16 +66,30 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_
         rotate = rotate && !is_v;
     }
 
-    float a[MAX_HEAD_DIM / 64], b[MAX_HEAD_DIM / 64];  // pairs (i, i + d/2), i = lane + 32 n
+    // The first `rot` values of the head are rotated in pairs (i, i + rot/2), i = lane + 32 n; the values from
+    // `rot` on (none when the whole head is rotated, as in Qwen3) are normalised and pass through.
+    const int rhalf = rot >> 1;
+    float a[MAX_HEAD_DIM / 64], b[MAX_HEAD_DIM / 64], c[MAX_HEAD_DIM / 32];
     float sq = 0.0f;
 #pragma unroll
     for (int n = 0; n < MAX_HEAD_DIM / 64; ++n) {
         const int i = lane + 32 * n;
         a[n] = b[n] = 0.0f;
-        if (i < half) {
+        if (i < rhalf) {
             a[n] = to_f32<T>(src[i]);
-            b[n] = to_f32<T>(src[i + half]);
+            b[n] = to_f32<T>(src[i + rhalf]);
             sq += a[n] * a[n] + b[n] * b[n];
+        }
+    }
+    if (rot < d) {
+#pragma unroll
+        for (int n = 0; n < MAX_HEAD_DIM / 32; ++n) {
+            const int i = rot + lane + 32 * n;
+            c[n] = 0.0f;
+            if (i < d) {
+                c[n] = to_f32<T>(src[i]);
+                sq += c[n] * c[n];
+            }
         }
     }
     if (norm_w != nullptr) {
@@ -84,24 +97,38 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_
 #pragma unroll
         for (int n = 0; n < MAX_HEAD_DIM / 64; ++n) {
             const int i = lane + 32 * n;
-            if (i < half) {
+            if (i < rhalf) {
                 a[n] = round_to<T>(round_to<T>(a[n] * inv) * norm_w[i]);
-                b[n] = round_to<T>(round_to<T>(b[n] * inv) * norm_w[i + half]);
+                b[n] = round_to<T>(round_to<T>(b[n] * inv) * norm_w[i + rhalf]);
+            }
+        }
+        if (rot < d) {
+#pragma unroll
+            for (int n = 0; n < MAX_HEAD_DIM / 32; ++n) {
+                const int i = rot + lane + 32 * n;
+                if (i < d) c[n] = round_to<T>(round_to<T>(c[n] * inv) * norm_w[i]);
             }
         }
     }
 #pragma unroll
     for (int n = 0; n < MAX_HEAD_DIM / 64; ++n) {
         const int i = lane + 32 * n;
-        if (i < half) {
+        if (i < rhalf) {
             float x = a[n], y = b[n];
             if (rotate) {
-                const float c = cos_tab[(int64_t)pos * half + i], s = sin_tab[(int64_t)pos * half + i];
-                x = a[n] * c - b[n] * s;
-                y = b[n] * c + a[n] * s;
+                const float cs = cos_tab[(int64_t)pos * rhalf + i], sn = sin_tab[(int64_t)pos * rhalf + i];
+                x = a[n] * cs - b[n] * sn;
+                y = b[n] * cs + a[n] * sn;
             }
             dst[i] = from_f32<T>(x);
-            dst[i + half] = from_f32<T>(y);
+            dst[i + rhalf] = from_f32<T>(y);
+        }
+    }
+    if (rot < d) {
+#pragma unroll
+        for (int n = 0; n < MAX_HEAD_DIM / 32; ++n) {
+            const int i = rot + lane + 32 * n;
+            if (i < d) dst[i] = from_f32<T>(c[n]);
         }
     }
 }
@@ -244,11 +271,13 @@ template <typename T>
 int qkv_prepare_launch(const T* qkv, T* q_out, T* k_pages, T* v_pages, const float* q_norm_w, const float* k_norm_w,
                        const float* cos_tab, const float* sin_tab, const int* token_seq, const int* token_pos,
                        const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps,
-                       int write_kv, cudaStream_t stream) {
+                       int write_kv, int rot, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (d <= 0 || d % 2 != 0 || d > MAX_HEAD_DIM || nq <= 0 || nkv <= 0) return Q3_ERR_BAD_SIZE;
+    if (rot <= 0) rot = d;                       // the whole head is rotated
+    if (rot % 2 != 0 || rot > d) return Q3_ERR_BAD_SIZE;
     constexpr int VEC = Pack<T>::N;
-    if (n_tokens >= 64 && (d / 2) % VEC == 0 && (d / 2) / VEC <= 32 && aligned16(qkv) && aligned16(q_out) &&
+    if (rot == d && n_tokens >= 64 && (d / 2) % VEC == 0 && (d / 2) / VEC <= 32 && aligned16(qkv) && aligned16(q_out) &&
         aligned16(k_pages) && aligned16(v_pages)) {
         const int hpw = 32 / ((d / 2) / VEC);
         const int64_t n_warps = (n_tokens * (nq + 2 * nkv) + hpw - 1) / hpw;
@@ -262,7 +291,7 @@ int qkv_prepare_launch(const T* qkv, T* q_out, T* k_pages, T* v_pages, const flo
     const int warps = 4;
     const dim3 grid((nq + 2 * nkv + warps - 1) / warps, (unsigned)n_tokens);
     return (int)q3_launch(qkv_prepare_kernel<T>, grid, dim3(warps * 32), 0, stream, qkv, q_out, k_pages, v_pages, q_norm_w,
-                          k_norm_w, cos_tab, sin_tab, token_seq, token_pos, page_table, pages_per_seq, nq, nkv, d, eps, write_kv);
+                          k_norm_w, cos_tab, sin_tab, token_seq, token_pos, page_table, pages_per_seq, nq, nkv, d, eps, write_kv, rot);
 }
 
 template <typename T>
@@ -284,10 +313,10 @@ int attention_generic_launch(const T* q, const T* k_pages, const T* v_pages, T* 
                                           const float* q_norm_w, const float* k_norm_w, const float* cos_tab,         \
                                           const float* sin_tab, const int* token_seq, const int* token_pos,           \
                                           const int* page_table, int pages_per_seq, int64_t n_tokens, int nq,         \
-                                          int nkv, int d, float eps, int write_kv, void* stream) {                   \
+                                          int nkv, int d, float eps, int write_kv, int rotary_dim, void* stream) {   \
         return qkv_prepare_launch<T>((const T*)qkv, (T*)q_out, (T*)k_pages, (T*)v_pages, q_norm_w, k_norm_w, cos_tab, \
                                      sin_tab, token_seq, token_pos, page_table, pages_per_seq, n_tokens, nq, nkv, d,  \
-                                     eps, write_kv, (cudaStream_t)stream);                                            \
+                                     eps, write_kv, rotary_dim, (cudaStream_t)stream);                                \
     }                                                                                                                 \
     Q3_EXPORT int q3_attention_generic_##SUFFIX(const void* q, const void* k_pages, const void* v_pages, void* out,   \
                                                 const int* token_seq, const int* token_pos, const int* page_table,    \

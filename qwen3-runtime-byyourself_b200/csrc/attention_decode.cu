@@ -89,13 +89,15 @@ __device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) 
 }
 
 // One head vector of the projection output, normalised (if `norm_w`) and rotated (if `cos_tab`), by one warp:
-// lane owns the pairs (i, i + D/2), i = lane + 32 n, exactly as qkv_prepare does (attention.cu), so the values
-// are the same to the bit.  dst: D bf16.
+// the first `rot` values are rotated in pairs (i, i + rot/2), i = lane + 32 n, the values from `rot` on (none when
+// the whole head is rotated) pass through - exactly as qkv_prepare does (attention.cu), so the values are the same
+// to the bit.  dst: D bf16.
 __device__ __forceinline__ void prepare_head(const bf16* __restrict__ src, bf16* dst, const float* __restrict__ norm_w,
                                              const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int pos,
-                                             float eps, int lane) {
-    constexpr int HALF = D / 2, ITER = (HALF + 31) / 32;
-    float a[ITER], b[ITER], wa[ITER], wb[ITER], cs[ITER], sn[ITER];
+                                             float eps, int rot, int lane) {
+    constexpr int ITER = (D / 2 + 31) / 32, REST = (D + 31) / 32;
+    const int rhalf = rot >> 1;
+    float a[ITER], b[ITER], wa[ITER], wb[ITER], cs[ITER], sn[ITER], c[REST], wc[REST];
     // every load first (they do not depend on one another), then the arithmetic
 #pragma unroll
     for (int n = 0; n < ITER; ++n) {
@@ -103,22 +105,38 @@ __device__ __forceinline__ void prepare_head(const bf16* __restrict__ src, bf16*
         a[n] = b[n] = 0.0f;
         wa[n] = wb[n] = cs[n] = 1.0f;
         sn[n] = 0.0f;
-        if (i < HALF) {
+        if (i < rhalf) {
             a[n] = __bfloat162float(src[i]);
-            b[n] = __bfloat162float(src[i + HALF]);
+            b[n] = __bfloat162float(src[i + rhalf]);
             if (norm_w != nullptr) {
                 wa[n] = norm_w[i];
-                wb[n] = norm_w[i + HALF];
+                wb[n] = norm_w[i + rhalf];
             }
             if (cos_tab != nullptr) {
-                cs[n] = cos_tab[(int64_t)pos * HALF + i];
-                sn[n] = sin_tab[(int64_t)pos * HALF + i];
+                cs[n] = cos_tab[(int64_t)pos * rhalf + i];
+                sn[n] = sin_tab[(int64_t)pos * rhalf + i];
+            }
+        }
+    }
+    if (rot < D) {
+#pragma unroll
+        for (int n = 0; n < REST; ++n) {
+            const int i = rot + lane + 32 * n;
+            c[n] = 0.0f;
+            wc[n] = 1.0f;
+            if (i < D) {
+                c[n] = __bfloat162float(src[i]);
+                if (norm_w != nullptr) wc[n] = norm_w[i];
             }
         }
     }
     float sq = 0.0f;
 #pragma unroll
     for (int n = 0; n < ITER; ++n) sq += a[n] * a[n] + b[n] * b[n];      // lanes beyond the head add zeros
+    if (rot < D) {
+#pragma unroll
+        for (int n = 0; n < REST; ++n) sq += c[n] * c[n];
+    }
     if (norm_w != nullptr) {
         const float inv = rsqrtf(warp_sum(sq) / (float)D + eps);
 #pragma unroll
@@ -126,18 +144,29 @@ __device__ __forceinline__ void prepare_head(const bf16* __restrict__ src, bf16*
             a[n] = round_to<bf16>(round_to<bf16>(a[n] * inv) * wa[n]);
             b[n] = round_to<bf16>(round_to<bf16>(b[n] * inv) * wb[n]);
         }
+        if (rot < D) {
+#pragma unroll
+            for (int n = 0; n < REST; ++n) c[n] = round_to<bf16>(round_to<bf16>(c[n] * inv) * wc[n]);
+        }
     }
 #pragma unroll
     for (int n = 0; n < ITER; ++n) {
         const int i = lane + 32 * n;
-        if (i < HALF) {
+        if (i < rhalf) {
             float x = a[n], y = b[n];
             if (cos_tab != nullptr) {
                 x = a[n] * cs[n] - b[n] * sn[n];
                 y = b[n] * cs[n] + a[n] * sn[n];
             }
             dst[i] = __float2bfloat16_rn(x);
-            dst[i + HALF] = __float2bfloat16_rn(y);
+            dst[i + rhalf] = __float2bfloat16_rn(y);
+        }
+    }
+    if (rot < D) {
+#pragma unroll
+        for (int n = 0; n < REST; ++n) {
+            const int i = rot + lane + 32 * n;
+            if (i < D) dst[i] = __float2bfloat16_rn(c[n]);
         }
     }
 }
@@ -151,6 +180,7 @@ struct FusedArgs {
     const float* cos_tab;          // [positions, D/2] or null
     const float* sin_tab;
     float eps;
+    int rot;                       // the first `rot` values of a head are rotated (the head size: all of them)
     int write_kv;                  // 0: the layer reads another layer's cache, which holds the new key and value already
 };
 
@@ -207,11 +237,11 @@ decode_split_kernel(const bf16* __restrict__ q, const bf16* k_pages, const bf16*
         const bf16* row = fused.qkv + (int64_t)t * (nq + 2 * nkv) * D;
         for (int r = warp; r < G; r += WARPS)
             prepare_head(row + (int64_t)(kvh * G + r) * D, prep + r * D, fused.q_norm_w, fused.cos_tab, fused.sin_tab, pos,
-                         fused.eps, lane);
+                         fused.eps, fused.rot, lane);
         if (owner) {
             if (warp == (G % WARPS))
                 prepare_head(row + (int64_t)(nq + kvh) * D, prep + 16 * D, fused.k_norm_w, fused.cos_tab, fused.sin_tab, pos,
-                             fused.eps, lane);
+                             fused.eps, fused.rot, lane);
             if (warp == ((G + 1) % WARPS))
                 for (int i = lane; i < D; i += 32) prep[17 * D + i] = row[(int64_t)(nq + nkv + kvh) * D + i];
         }
@@ -470,15 +500,18 @@ Q3_EXPORT int q3_attention_decode_bf16(const void* q, const void* k_pages, const
 }
 
 // The whole attention of a decode step in one launch (see the top of the file): `qkv` is the projection output
-// [tokens, (nq + 2 nkv) * head size]; norm weights and rotation tables may be null; `n_splits` <= 8.
+// [tokens, (nq + 2 nkv) * head size]; norm weights and rotation tables ([positions, rotary_dim / 2]) may be null;
+// `rotary_dim` 0 = the head size; `n_splits` <= 8.
 Q3_EXPORT int q3_attention_decode_fused_bf16(const void* qkv, void* k_pages, void* v_pages, void* out, const float* q_norm_w,
                                              const float* k_norm_w, const float* cos_tab, const float* sin_tab, float eps,
                                              const int* token_seq, const int* token_pos, const int* page_table,
                                              int pages_per_seq, int64_t n_tokens, int nq, int nkv, float scale, int window,
-                                             int n_splits, int write_kv, void* stream_) {
+                                             int n_splits, int write_kv, int rotary_dim, void* stream_) {
     if (n_tokens <= 0) return 0;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || n_splits <= 0 || n_splits > MAX_CLUSTER) return Q3_ERR_BAD_SIZE;
     if ((cos_tab == nullptr) != (sin_tab == nullptr)) return Q3_ERR_BAD_SIZE;
+    if (rotary_dim <= 0) rotary_dim = D;
+    if (rotary_dim % 2 != 0 || rotary_dim > D) return Q3_ERR_BAD_SIZE;
     if (n_tokens > 65535 || nkv > 65535) return Q3_ERR_TOO_LARGE;
     if (!aligned16(qkv) || !aligned16(k_pages) || !aligned16(v_pages)) return Q3_ERR_MISALIGNED;
     cudaStream_t stream = (cudaStream_t)stream_;
@@ -493,6 +526,7 @@ Q3_EXPORT int q3_attention_decode_fused_bf16(const void* qkv, void* k_pages, voi
     fused.cos_tab = cos_tab;
     fused.sin_tab = sin_tab;
     fused.eps = eps;
+    fused.rot = rotary_dim;
     fused.write_kv = write_kv;
     const dim3 grid(n_splits, nkv, (unsigned)n_tokens);
     return (int)q3_launch_cluster(decode_split_kernel<true>, grid, dim3(WARPS * 32), (size_t)SMEM_FUSED, stream, dim3(n_splits, 1, 1),

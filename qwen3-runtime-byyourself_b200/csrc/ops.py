@@ -291,6 +291,15 @@ def gemm_bf16_any_width(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> 
 
 
 # ------------------------------------------------------------------ attention
+def _rotary_dim(cos, sin, d: int) -> int:
+    """How many leading values of a head the tables rotate: twice their width (the head size without tables)."""
+    if cos is None:
+        return d
+    if sin is None or cos.shape != sin.shape or cos.dim() != 2 or 2 * cos.shape[1] > d:
+        raise KernelError("rotation tables are [positions, rotary_dim / 2] with rotary_dim <= head_dim")
+    return 2 * cos.shape[1]
+
+
 def qkv_prepare(qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, cos, sin, token_seq, token_pos, page_table,
                 n_tokens: int, nq: int, nkv: int, d: int, eps: float, write_kv: bool = True):
     """Per-head norm of q and k, rotation, and the write of k and v into the cache pages
@@ -300,14 +309,15 @@ def qkv_prepare(qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, cos, sin, toke
         raise KernelError(f"head_dim {d} is not supported: multiples of 16 up to 256")
     if qkv.shape[-1] != (nq + 2 * nkv) * d or k_pages.dtype != qkv.dtype or k_pages.shape[1:] != (nkv, PAGE_TOKENS, d):
         raise KernelError("qkv_prepare: shapes do not fit")
+    rot = _rotary_dim(cos, sin, d)
     fn = _fn("attention.cu", f"q3_qkv_prepare_{s}",
-             [c_void_p] * 11 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_void_p])
+             [c_void_p] * 11 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
     _check(fn(_dev(qkv, "qkv"), _dev(q_out, "q_out", qkv.dtype), _dev(k_pages, "k_pages"), _dev(v_pages, "v_pages"),
               _ptr(q_norm_w, "q_norm_w", torch.float32), _ptr(k_norm_w, "k_norm_w", torch.float32),
               _ptr(cos, "cos", torch.float32), _ptr(sin, "sin", torch.float32),
               _dev(token_seq, "token_seq", torch.int32), _dev(token_pos, "token_pos", torch.int32),
               _dev(page_table, "page_table", torch.int32), page_table.shape[-1], n_tokens, nq, nkv, d, float(eps),
-              int(bool(write_kv)), _stream()), "qkv_prepare")
+              int(bool(write_kv)), rot, _stream()), "qkv_prepare")
     return q_out
 
 
@@ -399,14 +409,15 @@ def attention_decode_fused(qkv, k_pages, v_pages, out, q_norm_w, k_norm_w, cos, 
     if qkv.shape[-1] != (nq + 2 * nkv) * d or k_pages.shape[1:] != (nkv, PAGE_TOKENS, d) or out.shape[-1] != nq * d:
         raise KernelError("attention_decode_fused: shapes do not fit")
     fn = _fn("attention_decode.cu", "q3_attention_decode_fused_bf16",
-             [c_void_p] * 8 + [c_float] + [c_void_p] * 3 + [c_int, c_int64, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
+             [c_void_p] * 8 + [c_float] + [c_void_p] * 3 + [c_int, c_int64, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
+                                                            c_void_p],
              defines=(f"Q3_HEAD_DIM={d}",))
     _check(fn(_dev(qkv, "qkv"), _dev(k_pages, "k_pages", torch.bfloat16), _dev(v_pages, "v_pages", torch.bfloat16),
               _dev(out, "out", torch.bfloat16), _ptr(q_norm_w, "q_norm_w", torch.float32), _ptr(k_norm_w, "k_norm_w", torch.float32),
               _ptr(cos, "cos", torch.float32), _ptr(sin, "sin", torch.float32), float(eps),
               _dev(token_seq, "token_seq", torch.int32), _dev(token_pos, "token_pos", torch.int32),
               _dev(page_table, "page_table", torch.int32), page_table.shape[-1], n_tokens, nq, nkv, float(scale),
-              int(window or 0), int(n_splits), int(bool(write_kv)), _stream()), "attention_decode_fused")
+              int(window or 0), int(n_splits), int(bool(write_kv)), _rotary_dim(cos, sin, d), _stream()), "attention_decode_fused")
     return out
 
 

@@ -52,14 +52,14 @@ int q3_place_rows(const void* src, int src_kind, void* dst, int dst_kind, int64_
                   int64_t dst_block_stride, int64_t dst_row0, void* stream);
 
 /* ---- attention.cu: every head size in steps of 16 up to 256, float32 and bfloat16 ------------------------ */
-/* per-head RMSNorm of q and k (weights may be null), rotation (tables [positions, d/2] may be null), and the
-   write of k and v into their pages (write_kv = 0: q only) */
+/* per-head RMSNorm of q and k (weights may be null), rotation of the first rotary_dim values of a head (0: all of
+   them; tables [positions, rotary_dim/2], may be null), and the write of k and v into their pages (write_kv = 0: q only) */
 int q3_qkv_prepare_f32(const void* qkv, void* q_out, void* k_pages, void* v_pages, const float* q_norm_w, const float* k_norm_w,
                        const float* cos_tab, const float* sin_tab, const int* token_seq, const int* token_pos, const int* page_table,
-                       int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps, int write_kv, void* stream);
+                       int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps, int write_kv, int rotary_dim, void* stream);
 int q3_qkv_prepare_bf16(const void* qkv, void* q_out, void* k_pages, void* v_pages, const float* q_norm_w, const float* k_norm_w,
                         const float* cos_tab, const float* sin_tab, const int* token_seq, const int* token_pos, const int* page_table,
-                        int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps, int write_kv, void* stream);
+                        int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps, int write_kv, int rotary_dim, void* stream);
 /* causal grouped-query attention of every token over its sequence's pages; window 0 = every key */
 int q3_attention_generic_f32(const void* q, const void* k_pages, const void* v_pages, void* out, const int* token_seq,
                              const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,
@@ -80,7 +80,7 @@ int q3_attention_decode_bf16(const void* q, const void* k_pages, const void* v_p
 int q3_attention_decode_fused_bf16(const void* qkv, void* k_pages, void* v_pages, void* out, const float* q_norm_w,
                                    const float* k_norm_w, const float* cos_tab, const float* sin_tab, float eps, const int* token_seq,
                                    const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv,
-                                   float scale, int window, int n_splits, int write_kv, void* stream);
+                                   float scale, int window, int n_splits, int write_kv, int rotary_dim, void* stream);
 
 /* ---- attention_prefill.cu, attention_prefill_tc.cu (-DQ3_HEAD_DIM): prompts, bfloat16 --------------------- */
 int q3_attention_prefill_head_dim(void);

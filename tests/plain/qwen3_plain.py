@@ -76,12 +76,15 @@ def rope_table(n_positions, head_dim, theta):
 
 def apply_rope(x, positions, cos, sin, rnd=identity):
     """Half-split rotation of the pairs (i, i+d/2) of every head.
-    x: [T, heads, d].  src/ops/rope.cu:60-84"""
-    half = x.shape[-1] // 2
+    x: [T, heads, d].  src/ops/rope.cu:60-84
+    Tables narrower than d/2 (not a Qwen3 option: the reference rotates the whole head; it exists for the
+    tests of the rotation kernels alone) rotate only the first 2 * width values, in pairs (i, i + width),
+    and leave the rest as they are."""
+    half = cos.shape[-1]
     c = cos[positions][:, None, :]
     s = sin[positions][:, None, :]
-    first, second = x[..., :half], x[..., half:]
-    return rnd(np.concatenate([first * c - second * s, second * c + first * s], axis=-1))
+    first, second, rest = x[..., :half], x[..., half:2 * half], x[..., 2 * half:]
+    return rnd(np.concatenate([first * c - second * s, second * c + first * s, rest], axis=-1))
 
 
 def gqa_attention(q, k, v, rnd=identity, window=None):

@@ -464,6 +464,81 @@ def test_decode_attention_fused_kernel(nq, nkv, d):
         ops.attention_decode_fused(qkv_d, kp, vp, out2, *args, 9)
 
 
+@pytest.mark.parametrize("nq,nkv,d,rot", [(4, 2, 64, 32), (8, 1, 128, 64), (6, 3, 48, 16), (5, 5, 80, 2), (2, 2, 256, 254),
+                                          (3, 1, 96, 96)])
+def test_partial_rotation_stays_fused(nq, nkv, d, rot):
+    """Tables of width rot/2 rotate only the first `rot` values of a head, in pairs (i, i + rot/2); the rest is
+    normalised and passes through.  The prepare kernel in 32-bit and in bfloat16 (a prompt of more and of fewer
+    than 64 tokens) and the one-launch decode attention agree with the plain float64 norm and rotation; the decode
+    step's new key is the one the prepare kernel would have written, to the bit.  The inputs make a fault show: the
+    values from `rot` on are ten times larger than the rotated ones, so rotating or dropping one of them is far
+    outside the tolerance."""
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(d + rot)
+    eps, theta = 3e-6, 777.0
+    lengths = [150, 9]
+    cos, sin = plain.rope_table(max(lengths) + 1, rot, theta)
+    assert cos.shape[1] == rot // 2
+    cos_d, sin_d = dev(cos, "float32"), dev(sin, "float32")
+    qw, kw = 1 + rng.normal(0, 0.1, d), 1 + rng.normal(0, 0.1, d)
+    qw_d, kw_d = dev(qw, "float32"), dev(kw, "float32")
+    qw, kw = qw_d.double().cpu().numpy(), kw_d.double().cpu().numpy()
+    full = [rng.normal(0, 1, (n + 1, nq + 2 * nkv, d)) for n in lengths]      # the last row is the decode step's
+    for x in full:
+        x[..., rot:] *= 10.0
+    full = [x.reshape(x.shape[0], -1) for x in full]
+    seq = np.concatenate([np.full(n, s) for s, n in enumerate(lengths)]).astype(np.int32)
+    pos = np.concatenate([np.arange(n) for n in lengths]).astype(np.int32)
+    N = len(seq)
+    seq_d, pos_d = torch.as_tensor(seq).cuda(), torch.as_tensor(pos).cuda()
+    for dtype in ("float32", "bfloat16"):
+        rnd = plain.identity if dtype == "float32" else plain.round_bf16
+        table, kp, vp = paged_case(rng, [n + 1 for n in lengths], nkv, d, dtype)
+        table_d = torch.as_tensor(table).cuda()
+        qkv = dev(np.concatenate([x[:-1] for x in full]), dtype)
+        q = torch.empty(N, nq * d, dtype=DT[dtype], device="cuda")
+        ops.qkv_prepare(qkv, q, kp, vp, qw_d, kw_d, cos_d, sin_d, seq_d, pos_d, table_d, N, nq, nkv, d, eps)
+        got_q = back(q)
+        row = 0
+        wants = []
+        for s, n in enumerate(lengths):
+            x = stored(full[s], dtype)
+            qs = x[:, :nq * d].reshape(n + 1, nq, d)
+            ks = x[:, nq * d:(nq + nkv) * d].reshape(n + 1, nkv, d)
+            vs = x[:, (nq + nkv) * d:].reshape(n + 1, nkv, d)
+            p = np.arange(n + 1)
+            qs = plain.apply_rope(plain.rms_norm(qs, qw, eps, rnd), p, cos, sin, rnd)
+            ks = plain.apply_rope(plain.rms_norm(ks, kw, eps, rnd), p, cos, sin, rnd)
+            wants.append((qs, ks, vs))
+            scale = np.max(np.abs(qs))
+            assert np.max(np.abs(got_q[row:row + n] - qs[:n].reshape(n, -1))) <= tol(dtype, 3) * scale, (dtype, s)
+            for t in (0, n - 1, min(n - 1, 64)):
+                page = table[s, t // 64]
+                assert np.max(np.abs(back(kp[page, :, t % 64]) - ks[t])) <= tol(dtype, 3) * scale, (dtype, s, t)
+                np.testing.assert_array_equal(back(vp[page, :, t % 64]), vs[t])
+            row += n
+    # the decode step of both sequences in one launch (bfloat16; kp, vp and wants are the bfloat16 ones)
+    B = len(lengths)
+    step = dev(np.stack([x[-1] for x in full]), "bfloat16")
+    dseq = torch.arange(B, dtype=torch.int32, device="cuda")
+    dpos = torch.as_tensor(lengths, dtype=torch.int32).cuda()
+    out = torch.zeros(B, nq * d, dtype=torch.bfloat16, device="cuda")
+    kp2, vp2 = kp.clone(), vp.clone()
+    ops.attention_decode_fused(step, kp, vp, out, qw_d, kw_d, cos_d, sin_d, eps, dseq, dpos, table_d, B, nq, nkv, d, d ** -0.5,
+                               None, 2)
+    q2 = torch.empty(B, nq * d, dtype=torch.bfloat16, device="cuda")
+    ops.qkv_prepare(step, q2, kp2, vp2, qw_d, kw_d, cos_d, sin_d, dseq, dpos, table_d, B, nq, nkv, d, eps)
+    assert torch.equal(kp, kp2) and torch.equal(vp, vp2)
+    for s, n in enumerate(lengths):
+        qs, ks, vs = wants[s]
+        want = plain.gqa_attention(qs, ks, vs)[n].reshape(-1)
+        assert np.max(np.abs(back(out[s]) - want)) <= 2.5e-2 * max(1.0, np.max(np.abs(vs))), s
+    # tables that are wider than the head are refused
+    wide = torch.zeros(8, d // 2 + 1, dtype=torch.float32, device="cuda")
+    with pytest.raises(ops.KernelError):
+        ops.qkv_prepare(step, q2, kp2, vp2, qw_d, kw_d, wide, wide, dseq, dpos, table_d, B, nq, nkv, d, eps)
+
+
 @pytest.mark.parametrize("nq,nkv,d", [(4, 2, 16), (8, 1, 32), (6, 3, 48), (8, 2, 128), (2, 2, 256), (5, 5, 80)])
 @pytest.mark.parametrize("window", [None, 90])
 def test_prefill_attention_tiled_kernel(nq, nkv, d, window):

@@ -467,6 +467,85 @@ def test_toy_routed_feed_forward_and_toy_position_encoding():
                     assert np.max(np.abs(got[(rid, p)] - want[p])) <= 1e-4, (rid, p)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rotation_of_a_part_of_the_head_stays_on_the_fused_kernels(dtype):
+    """A rotary encoding that turns only the first `rotary_dim` values of a head (a parameter of the position part,
+    not an option of this architecture) in layers 0 and 2, the whole head in layer 1: the tables are
+    [positions, rotary_dim/2], the prepare kernel and the one-launch decode attention take them as they are, and
+    whole prompts, the last tokens one by one and unequal batches agree with the plain model."""
+    import qwen3_b200 as q
+    from qwen3_b200.csrc import ops
+    from qwen3_b200.engine.engine import Engine
+    from qwen3_b200.parts import build_part
+    from test_engine_gpu import run_steps
+    cfg = tiny("B")
+    config = q.config_from_dict(cfg)
+    plan = config.plan()
+    d, theta = cfg["head_dim"], cfg["rope_theta"]
+    rot = {0: d // 2, 1: d, 2: 2}
+    rope = build_part("position", q.PartSpec("rope", {"head_dim": d, "theta": theta, "max_positions": 50, "rotary_dim": rot[0]}))
+    rope.prepare(50, "cuda")
+    cos, sin = plain.rope_table(50, rot[0], theta)
+    np.testing.assert_array_equal(rope.cos.double().cpu().numpy(), cos)
+    rng = np.random.default_rng(2)
+    qh = torch.tensor(rng.normal(0, 1, (3, 2, d)), dtype=dtype, device="cuda")
+    kh = torch.tensor(rng.normal(0, 1, (3, 1, d)), dtype=dtype, device="cuda")
+    pos = torch.tensor([0, 7, 49], dtype=torch.int32, device="cuda")
+    rnd = plain.identity if dtype == torch.float32 else plain.round_bf16
+    want_q = plain.apply_rope(qh.double().cpu().numpy(), pos.cpu().numpy(), cos, sin, rnd)
+    rope.apply_(qh, kh, pos)
+    np.testing.assert_allclose(qh.double().cpu().numpy(), want_q, atol=3e-5 if dtype == torch.float32 else 3e-2, rtol=0)
+    assert np.array_equal(qh[..., rot[0]:].double().cpu().numpy(), want_q[..., rot[0]:])       # the rest is untouched
+
+    layers = []
+    for i, layer in enumerate(plan.layers):
+        position = q.PartSpec("rope", dict(layer.mixer.params["position"].params, rotary_dim=rot[i]))
+        layers.append(dataclasses.replace(layer, mixer=q.PartSpec("gqa_attention", dict(layer.mixer.params, position=position))))
+    plan = dataclasses.replace(plan, layers=layers)
+    model = q.build_model(plan)
+    tensors = q.random_weights(model.weight_specs(), seed=21, dtype=torch.bfloat16)
+    weights = {k: v.double().numpy() for k, v in tensors.items()}
+    model.bind(dict(tensors), dtype, "cuda")
+
+    def plain_forward(tokens, rnd):
+        x = plain.embedding(tokens, weights["model.embed_tokens.weight"])
+        T = len(tokens)
+        for layer in range(cfg["num_hidden_layers"]):
+            cos, sin = plain.rope_table(T, rot[layer], theta)
+            x = plain.decoder_layer(x, np.arange(T), cfg, weights, layer, cos, sin, rnd)
+        x = plain.rms_norm(x, weights["model.norm.weight"], cfg["rms_norm_eps"], rnd)
+        return plain.linear(x, plain.output_weight(cfg, weights))
+
+    calls = {"prepare": 0, "fused": 0}
+    real_prepare, real_fused = ops.qkv_prepare, ops.attention_decode_fused
+
+    def count(name, fn):
+        def wrapped(*a, **k):
+            calls[name] += 1
+            return fn(*a, **k)
+        return wrapped
+    rng = np.random.default_rng(9)
+    requests = {f"r{i}": [int(t) for t in rng.integers(0, cfg["vocab_size"], n)] for i, n in enumerate([100, 40, 139, 5])}
+    ops.qkv_prepare, ops.attention_decode_fused = count("prepare", real_prepare), count("fused", real_fused)
+    try:
+        for builder in (schedules.whole, lambda r: schedules.tail_one_by_one(r, 32),
+                        lambda r: schedules.batched(r, {"r0": 70, "r1": 1, "r2": 64, "r3": 5}, 2)):
+            steps, rows = builder(requests)
+            engine = Engine(model, config, max_tokens=schedules.peak_tokens(steps))
+            got = run_steps(engine, steps, rows)
+            for rid, toks in requests.items():
+                want = plain_forward(toks, plain.identity)
+                tol = 1e-4 if dtype == torch.float32 else \
+                    4.0 * float(np.max(np.abs(want - plain_forward(toks, plain.round_bf16)))) + 1e-6
+                for p in range(len(toks)):
+                    if (rid, p) in got:
+                        err = float(np.max(np.abs(got[(rid, p)] - want[p])))
+                        assert err <= tol, (rid, p, err, tol)
+    finally:
+        ops.qkv_prepare, ops.attention_decode_fused = real_prepare, real_fused
+    assert calls["prepare"] > 0 and (dtype == torch.float32 or calls["fused"] > 0)
+
+
 def test_linear_takes_every_form_of_the_product():
     """`linear` chooses among the library's products by the shape: the few-row kernel, weights first (K split
     over a cluster), tokens first on single SMs, tokens first on pairs of SMs, and the CUDA-core kernel for a
