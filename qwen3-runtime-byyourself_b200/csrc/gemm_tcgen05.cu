@@ -300,6 +300,48 @@ template <> __device__ __forceinline__ void store_run8<bf16>(bf16* p, const uint
 
 // GATED: W holds gate and up rows interleaved in blocks of eight (as the decode kernel's gated form);
 // the epilogue then writes round(silu(g)) * u, [M, N/2], instead of the raw product.
+// 32 consecutive columns (rows of W n0 + c ..) of one token's accumulator row, converted and stored; `row` points at
+// the token's first output of this tile.  GATED: the columns are gate[8] up[8] gate[8] up[8] of 16 features and
+// the output is round(silu(g)) * u with both rounded to bfloat16 first (src/ops/elementwise.cu:47-65).
+template <bool GATED, typename OutT>
+__device__ __forceinline__ void store_chunk32(const uint32_t (&r)[32], OutT* row, int c, int n0, bool token_valid, int N,
+                                              bool vec_ok) {
+    if (!token_valid) return;
+    if constexpr (GATED) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int n = n0 + c + h * 16;           // first gate column of this block
+            uint32_t packed[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float g = round_to<bf16>(__uint_as_float(r[h * 16 + e]));
+                const float u = round_to<bf16>(__uint_as_float(r[h * 16 + 8 + e]));
+                packed[e] = __float_as_uint(round_to<bf16>(g / (1.0f + expf(-g))) * u);
+            }
+            OutT* dst = row + ((c + h * 16) >> 1);
+            if (n + 16 <= N && vec_ok) {
+                store_run8<OutT>(dst, packed);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    if (n + 8 + e < N) dst[e] = to_out<OutT>(__uint_as_float(packed[e]));
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            const int n = n0 + c + j;
+            if (vec_ok && n + 8 <= N) {
+                store_run8<OutT>(row + c + j, r + j);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    if (n + e < N) row[c + j + e] = to_out<OutT>(__uint_as_float(r[j + e]));
+            }
+        }
+    }
+}
+
 template <int BN, int STAGES, bool GATED, typename OutT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -401,42 +443,7 @@ gemm_tcgen05_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((uint32_t)lane_base << 16) + buf * BN + (uint32_t)c, r);
                 tc_wait_ld();
-                if constexpr (GATED) {
-                    // columns c..c+31 = gate[8] up[8] gate[8] up[8] of 16 features (src/ops/elementwise.cu:47-65)
-                    if (m < M) {
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const int n = n0 + c + h * 16;           // first gate column of this block
-                            uint32_t packed[8];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                const float g = round_to<bf16>(__uint_as_float(r[h * 16 + e]));
-                                const float u = round_to<bf16>(__uint_as_float(r[h * 16 + 8 + e]));
-                                packed[e] = __float_as_uint(round_to<bf16>(g / (1.0f + expf(-g))) * u);
-                            }
-                            OutT* dst = row + ((c + h * 16) >> 1);
-                            if (n + 16 <= N && vec_ok) {
-                                store_run8<OutT>(dst, packed);
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 8; ++e)
-                                    if (n + 8 + e < N) dst[e] = to_out<OutT>(__uint_as_float(packed[e]));
-                            }
-                        }
-                    }
-                } else if (m < M) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        const int n = n0 + c + j;
-                        if (vec_ok && n + 8 <= N) {
-                            store_run8<OutT>(row + c + j, r + j);
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 8; ++e)
-                                if (n + e < N) row[c + j + e] = to_out<OutT>(__uint_as_float(r[j + e]));
-                        }
-                    }
-                }
+                store_chunk32<GATED, OutT>(r, row, c, n0, m < M, N, vec_ok);
             }
             tc_fence_before();
             __syncwarp();
@@ -479,9 +486,10 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, ui
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // Arrives, once the MMAs issued so far are done, at the barrier at this offset in both blocks of the pair.
-__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+// `mask`: the two blocks of the pair by their ranks in the cluster (3 for a cluster that is one pair).
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t mask = 3) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+                 ::"r"(bar), "h"(mask) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
@@ -595,42 +603,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((uint32_t)lane_base << 16) + buf * BN + (uint32_t)c, r);
                 tc_wait_ld();
-                if constexpr (GATED) {
-                    // columns c..c+31 = gate[8] up[8] gate[8] up[8] of 16 features (src/ops/elementwise.cu:47-65)
-                    if (m < M) {
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const int n = n0 + c + h * 16;           // first gate column of this block
-                            uint32_t packed[8];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                const float g = round_to<bf16>(__uint_as_float(r[h * 16 + e]));
-                                const float u = round_to<bf16>(__uint_as_float(r[h * 16 + 8 + e]));
-                                packed[e] = __float_as_uint(round_to<bf16>(g / (1.0f + expf(-g))) * u);
-                            }
-                            OutT* dst = row + ((c + h * 16) >> 1);
-                            if (n + 16 <= N && vec_ok) {
-                                store_run8<OutT>(dst, packed);
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 8; ++e)
-                                    if (n + 8 + e < N) dst[e] = to_out<OutT>(__uint_as_float(packed[e]));
-                            }
-                        }
-                    }
-                } else if (m < M) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        const int n = n0 + c + j;
-                        if (vec_ok && n + 8 <= N) {
-                            store_run8<OutT>(row + c + j, r + j);
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 8; ++e)
-                                if (n + e < N) row[c + j + e] = to_out<OutT>(__uint_as_float(r[j + e]));
-                        }
-                    }
-                }
+                store_chunk32<GATED, OutT>(r, row, c, n0, m < M, N, vec_ok);
             }
             tc_fence_before();
             __syncwarp();
@@ -640,6 +613,172 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     tc_fence_before();
     __syncwarp();
     cluster_sync();                                           // the peer reads this block's memory and barriers until here
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same tile on pairs of SMs with K split over the pairs of one cluster, for the shapes whose 256 x 256
+// tiles are too few (or just too many) for the 74 pairs of the GPU: a few hundred tokens, or a tile count
+// slightly above a whole number of waves.  A cluster of 2 S blocks is S pairs; pair s multiplies the K
+// range s of one tile, and the S partial accumulators meet over distributed shared memory: every block
+// finishes every S-th chunk of 32 columns; it sends the other chunks of its accumulator into the (by then
+// idle) stages of the blocks of its own parity that finish them - remote stores, which do not wait, where
+// remote loads took 1.8 us a round - and adds what it received to its own in pair order 0 .. S-1: a fixed
+// order, so the sum does not depend on which block computes it.  One tile per cluster, one accumulator.
+// Grid (2 S, tiles): the rank in the cluster is blockIdx.x; the token tile varies fastest in blockIdx.y.
+constexpr int SPLITK_CHUNK_BYTES = BM * 32 * 4;       // one parked chunk: 128 tokens x 32 columns of float32
+
+__device__ __forceinline__ uint32_t parked_addr(uint32_t base, int chunk, int row, int quad) {
+    // a thread only ever reads back what the thread of the same row wrote, so the layout is free: the 32 lanes of
+    // one store (one 16-byte quad each) fill 512 consecutive bytes, which the network between SMs moves whole
+    return base + (uint32_t)chunk * SPLITK_CHUNK_BYTES + (uint32_t)(row >> 5) * 4096u + (uint32_t)quad * 512u + (uint32_t)(row & 31) * 16u;
+}
+
+template <int STAGES, bool GATED, typename OutT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_pair_splitk_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                                OutT* __restrict__ Y, int M, int N, int K, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    constexpr int BN = 256, PAIR_M = 2 * BM, CHUNKS = BN / 32;
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = BN;
+    static_assert(6 * SPLITK_CHUNK_BYTES <= STAGES * STAGE_BYTES, "the received chunks reuse the stages (at most 3 senders x 2 or 2 x 3 or 1 x 4)");
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = base + STAGES * STAGE_BYTES;       // full[S], empty[S], acc_full, slot
+    const uint32_t bar_acc_full = bars + 2 * STAGES * 8, tmem_slot = bar_acc_full + 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank(), parity = rank & 1u, leader = rank & ~1u;
+    const int split = (int)(rank >> 1), splits = (int)(gridDim.x >> 1);
+    const int pairs_m = (M + PAIR_M - 1) / PAIR_M;
+    const int tile = blockIdx.y;
+    const int m0 = (tile % pairs_m) * PAIR_M + (int)parity * BM, n0 = (tile / pairs_m) * BN;
+    const int nkb_all = (K + BK - 1) / BK;
+    const int kb_begin = (int)(((int64_t)split * nkb_all) / splits), kb_end = (int)(((int64_t)(split + 1) * nkb_all) / splits);
+    const int nkb = kb_end - kb_begin;                       // the host keeps splits <= nkb_all: at least one step
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bars + s * 8, 1);
+            mbar_init(bars + (STAGES + s) * 8, 1);
+        }
+        mbar_init(bar_acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                           // the peers' barriers exist before anything signals them
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+    bool acc_ok = true;
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(bars + (STAGES + s) * 8, ((uint32_t)(i / STAGES) & 1u) ^ 1u)) { atomicExch(status, 1); break; }
+                const uint32_t a = base + s * STAGE_BYTES, b = a + A_BYTES;
+                const uint32_t full_in_leader = map_to_rank(bars + s * 8, leader);
+                if (parity == 0) mbar_expect_tx(bars + s * 8, 2 * STAGE_BYTES);         // both blocks' bytes
+                tma_load_2d_pair(b, &map_w, full_in_leader, (kb_begin + i) * BK, n0 + (int)parity * (BN / 2));
+                if (i == 0) pdl_wait();                       // the weights do not depend on the kernel before; X does
+                tma_load_2d_pair(a, &map_x, full_in_leader, (kb_begin + i) * BK, m0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && parity == 0) {
+            constexpr uint32_t idesc = make_idesc_mn(PAIR_M, BN);
+            const uint16_t mask = (uint16_t)(3u << leader);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(bars + s * 8, (uint32_t)(i / STAGES) & 1u)) { atomicExch(status, 2); break; }
+                tc_fence_after();
+                const uint32_t a = base + s * STAGE_BYTES, b = a + A_BYTES;
+                const uint64_t da = make_desc(a), db = make_desc(b);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    tc_mma_pair(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                tc_commit_pair(bars + (STAGES + s) * 8, mask);
+            }
+            tc_commit_pair(bar_acc_full, mask);               // accumulator complete (or abandoned)
+        }
+    } else {
+        acc_ok = mbar_wait(bar_acc_full, 0);
+        if (!acc_ok && lane == 0) atomicExch(status, 3);
+    }
+    tc_fence_before();
+    __syncwarp();
+    cluster_sync();                   // every pair's loads have landed and been consumed: the stages of all blocks are free
+    tc_fence_after();
+    const int lane_base = (warp & 3) * 32, row = lane_base + lane;
+    if (warp >= 2 && acc_ok) {
+        // send the chunks that another block finishes into that block's stages (remote stores do not wait)
+#pragma unroll 1
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int owner = c % splits;
+            if (owner == split) continue;
+            uint32_t r[32];
+            tc_ld32(tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(c * 32), r);
+            tc_wait_ld();
+            // slot of (sender, the owner's n-th chunk) in the owner: senders in pair order, the owner itself left out
+            const int slot = (split - (split > owner ? 1 : 0)) * ((CHUNKS + splits - 1) / splits) + c / splits;
+            const uint32_t dst_rank = (uint32_t)(2 * owner) + parity;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                asm volatile("st.shared::cluster.v4.b32 [%0], {%1,%2,%3,%4};"
+                             ::"r"(map_to_rank(parked_addr(base, slot, row, q), dst_rank)), "r"(r[4 * q]), "r"(r[4 * q + 1]),
+                               "r"(r[4 * q + 2]), "r"(r[4 * q + 3]) : "memory");
+        }
+    }
+    __syncwarp();
+    cluster_sync();                                           // every block holds the partials of its chunks
+
+    if (warp >= 2 && acc_ok) {
+        pdl_wait();                                           // no global write before this
+        const bool vec_ok = ((GATED ? (N >> 1) : N) % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15u) == 0);
+        const int m = m0 + row;
+        OutT* out_row = Y + (int64_t)m * (GATED ? (N >> 1) : N) + (GATED ? (n0 >> 1) : n0);
+#pragma unroll 1
+        for (int c = split; c < CHUNKS; c += splits) {
+            uint32_t own[32], r[32];
+            tc_ld32(tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(c * 32), own);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0u;           // 0.0f
+            for (int s = 0; s < splits; ++s) {                // pair order, whoever adds
+                if (s == split) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(own[j]));
+                } else {
+                    const int slot = (s - (s > split ? 1 : 0)) * ((CHUNKS + splits - 1) / splits) + c / splits;
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        float4 v;
+                        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                                     : "r"(parked_addr(base, slot, row, q)) : "memory");
+                        r[4 * q] = __float_as_uint(__uint_as_float(r[4 * q]) + v.x);
+                        r[4 * q + 1] = __float_as_uint(__uint_as_float(r[4 * q + 1]) + v.y);
+                        r[4 * q + 2] = __float_as_uint(__uint_as_float(r[4 * q + 2]) + v.z);
+                        r[4 * q + 3] = __float_as_uint(__uint_as_float(r[4 * q + 3]) + v.w);
+                    }
+                }
+            }
+            store_chunk32<GATED, OutT>(r, out_row, c * 32, n0, m < M, N, vec_ok);
+        }
+    }
+    tc_fence_before();
+    __syncwarp();
+    cluster_sync();                                           // the pair gives its tensor memory back together
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -729,6 +868,50 @@ int launch_pair(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int*
                                   stream, dim3(2, 1, 1), map_x, map_w, Y, M, N, K, status);
 }
 
+template <int STAGES, bool GATED, typename OutT>
+int launch_pair_splitk(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int splits, int* status, cudaStream_t stream) {
+    constexpr int SMEM = STAGES * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256;
+    static Q3PerDevice configured;
+    {
+        cudaError_t e = q3_allow_shared_memory(gemm_tcgen05_pair_splitk_kernel<STAGES, GATED, OutT>, SMEM, configured);
+        if (e != cudaSuccess) return (int)e;
+    }
+    CUtensorMap map_x, map_w;
+    if (!make_map(&map_x, X, M, K, BM) || !make_map(&map_w, W, N, K, 128)) return Q3_ERR_BAD_SIZE;
+    const int64_t tiles = (int64_t)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+    if (tiles > 65535) return Q3_ERR_TOO_LARGE;
+    return (int)q3_launch_cluster(gemm_tcgen05_pair_splitk_kernel<STAGES, GATED, OutT>, dim3(2 * splits, (unsigned)tiles), dim3(THREADS),
+                                  (size_t)SMEM, stream, dim3(2 * splits, 1, 1), map_x, map_w, Y, M, N, K, status);
+}
+
+// How many pairs of SMs run at the same time when a cluster is `splits` pairs (what the device can place).
+int pair_capacity(int splits) {
+    static int cached[64][5];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || splits < 1 || splits > 4) return 0;
+    if (cached[dev][splits] == 0) {
+        constexpr int SMEM = 6 * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256;
+        static Q3PerDevice configured;
+        auto kernel = gemm_tcgen05_pair_splitk_kernel<6, false, bf16>;
+        if (q3_allow_shared_memory(kernel, SMEM, configured) != cudaSuccess) return 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * splits, 1024);
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = SMEM;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2 * splits;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+        cached[dev][splits] = clusters * splits;
+    }
+    return cached[dev][splits];
+}
+
 }  // namespace
 
 // The prompt form: persistent blocks, 128 tokens x `tile_n` (128 or 256) rows of W per tile.
@@ -750,19 +933,29 @@ Q3_EXPORT int q3_gemm_tcgen05_prompt_bf16(const void* X, const void* W, void* Y,
 }
 
 // The prompt form on pairs of SMs: tiles of 256 tokens x 256 rows of W, each block of a pair loading half of
-// the W tile.  `gated` as below (bfloat16 output only).
+// the W tile.  `gated` as below (bfloat16 output only).  `splits` (1..4) > 1: K split over that many pairs of a
+// cluster, one tile per cluster.
 Q3_EXPORT int q3_gemm_tcgen05_pair_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int gated,
-                                        int* status, void* stream_) {
+                                        int splits, int* status, void* stream_) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 != 0 || (gated && (N % 16 != 0 || out_is_f32))) return Q3_ERR_BAD_SIZE;
+    if (K <= 0 || K % 8 != 0 || (gated && (N % 16 != 0 || out_is_f32)) || splits < 1 || splits > 4) return Q3_ERR_BAD_SIZE;
     if (!aligned16(X) || !aligned16(W)) return Q3_ERR_MISALIGNED;
     cudaStream_t stream = (cudaStream_t)stream_;
     const bf16* x = (const bf16*)X;
     const bf16* w = (const bf16*)W;
+    if (splits > (K + BK - 1) / BK) splits = (K + BK - 1) / BK;
+    if (splits > 1) {
+        if (gated) return launch_pair_splitk<6, true, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
+        return out_is_f32 ? launch_pair_splitk<6, false, float>(x, w, (float*)Y, M, N, K, splits, status, stream)
+                          : launch_pair_splitk<6, false, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
+    }
     if (gated) return launch_pair<6, true, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
     return out_is_f32 ? launch_pair<6, false, float>(x, w, (float*)Y, M, N, K, status, stream)
                       : launch_pair<6, false, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
 }
+
+// Pairs of SMs that run at once when K is split over `splits` pairs of a cluster (0: the device cannot place it).
+Q3_EXPORT int q3_gemm_tcgen05_pair_capacity(int splits) { return pair_capacity(splits); }
 
 // W [N, K] holds gate and up rows interleaved in blocks of eight; Y [M, N/2] = round(silu(g)) * u, bfloat16.
 Q3_EXPORT int q3_gemm_tcgen05_prompt_gated_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int* status,

@@ -563,22 +563,36 @@ def gemm_tcgen05_prompt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, til
     return out
 
 
-def gemm_tcgen05_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> torch.Tensor:
+def gemm_tcgen05_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False,
+                      splits: int = 1) -> torch.Tensor:
     """The prompt product on pairs of SMs (tcgen05 cta_group::2): tiles of 256 tokens by 256 rows of w, each
     block of a pair loading its own tokens and half of the w tile.  `gated`: w holds gate and up rows
-    interleaved in blocks of eight and out is [M, N/2] = round(silu(g)) * u."""
+    interleaved in blocks of eight and out is [M, N/2] = round(silu(g)) * u.  `splits` (1..4): K split over
+    that many pairs of one cluster, whose partial tiles are summed over distributed shared memory in a fixed
+    order (for shapes with too few tiles, or a tile count just above a whole number of waves)."""
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (M, N // 2 if gated else N) or K % 8 != 0 or (gated and N % 16 != 0):
         raise KernelError(f"gemm_tcgen05_pair: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
     if out.dtype not in ((torch.bfloat16,) if gated else (torch.bfloat16, torch.float32)):
         raise KernelError("gemm_tcgen05_pair: output must be bfloat16 (or float32 when not gated)")
+    if not 1 <= splits <= PAIR_MAX_SPLITS:
+        raise KernelError(f"gemm_tcgen05_pair: 1 to {PAIR_MAX_SPLITS} K ranges, not {splits}")
     fn = _fn("gemm_tcgen05.cu", "q3_gemm_tcgen05_pair_bf16",
-             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), M, N, K,
-              int(out.dtype == torch.float32), int(gated), _status_word(x.device).data_ptr(), _stream()),
+              int(out.dtype == torch.float32), int(gated), int(splits), _status_word(x.device).data_ptr(), _stream()),
            "gemm_tcgen05_pair")
     return out
+
+
+PAIR_MAX_SPLITS = 4
+
+
+def gemm_tcgen05_pair_capacity(splits: int) -> int:
+    """How many pairs of SMs of the current device run at once when a cluster is `splits` pairs (0: none fit)."""
+    fn = _fn_untimed("gemm_tcgen05.cu", "q3_gemm_tcgen05_pair_capacity", [c_int])
+    return int(fn(int(splits)))
 
 
 def gemm_tcgen05_prompt_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

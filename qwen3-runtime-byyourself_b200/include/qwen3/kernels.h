@@ -111,8 +111,10 @@ int q3_gemm_tcgen05_mid_splits(int N, int K, int M);
 int q3_gemm_tcgen05_prompt_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int tile_n, int* status,
                                 void* stream);
 int q3_gemm_tcgen05_prompt_gated_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int* status, void* stream);
-int q3_gemm_tcgen05_pair_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int gated, int* status,
-                              void* stream);
+/* splits 1..4: K split over that many pairs of SMs of one cluster (1: persistent pairs, no split) */
+int q3_gemm_tcgen05_pair_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int gated, int splits,
+                              int* status, void* stream);
+int q3_gemm_tcgen05_pair_capacity(int splits);
 
 /* ---- sampling.cu ------------------------------------------------------------------------------------------ */
 /* out[r] = index of the highest logit among the first `valid` (lowest id among equals, NaN as -inf) */

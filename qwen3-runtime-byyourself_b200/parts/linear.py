@@ -31,6 +31,27 @@ def set_bf16_kernel(fn: Optional[Callable]) -> None:
 # Microseconds per 64-wide K step of a tile and per block for its start and end, measured on B200.
 _STEP_US = {"pair": 0.33, "prompt128": 0.29, "weights_first": 0.40}
 _BLOCK_US = {"pair": 8.0, "prompt128": 5.0}
+# A tile with K split over the pairs of a cluster is not persistent: every wave pays the start of the stream and the
+# meeting of the partial tiles over distributed shared memory, and the launch a little more.
+_PAIR_SPLIT_WAVE_US, _PAIR_SPLIT_LAUNCH_US = 8.5, 2.5
+
+
+@functools.lru_cache(maxsize=4096)
+def pair_plan(M: int, N: int, K: int) -> tuple:
+    """(estimated microseconds, K ranges) of the pairs-of-SMs form: the number of K ranges per tile (1 = persistent
+    pairs, no split) whose waves of tiles x K steps cost least."""
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    nkb, tiles = -(-K // 64), -(-M // 256) * -(-N // 256)
+    best = (-(-tiles // (sms // 2)) * nkb * _STEP_US["pair"] + _BLOCK_US["pair"], 1)
+    for splits in range(2, ops.PAIR_MAX_SPLITS + 1):
+        capacity = ops.gemm_tcgen05_pair_capacity(splits)
+        if capacity <= 0 or splits > nkb or tiles > 65535:
+            continue
+        cost = (-(-tiles * splits // capacity) * (-(-nkb // splits) * _STEP_US["pair"] + _PAIR_SPLIT_WAVE_US)
+                + _PAIR_SPLIT_LAUNCH_US)
+        if cost < best[0]:
+            best = (cost, splits)
+    return best
 
 
 @functools.lru_cache(maxsize=4096)
@@ -47,7 +68,7 @@ def tcgen05_form(M: int, N: int, K: int, gated: bool = False) -> str:
     def waves(blocks, slots):
         return -(-blocks // slots)
 
-    cost = {"pair": waves(-(-M // 256) * -(-N // 256), sms // 2) * nkb * _STEP_US["pair"] + _BLOCK_US["pair"]}
+    cost = {"pair": pair_plan(M, N, K)[0]}
     if not gated:                                        # the gated epilogue exists for the 256-row tiles
         cost["prompt128"] = waves(-(-M // 128) * -(-N // 128), sms) * nkb * _STEP_US["prompt128"] + _BLOCK_US["prompt128"]
     if M <= 1024:
@@ -78,5 +99,5 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     if form == "weights_first":
         return ops.gemm_tcgen05_mid(x, w, out)
     if form == "pair":
-        return ops.gemm_tcgen05_pair(x, w, out)
+        return ops.gemm_tcgen05_pair(x, w, out, splits=pair_plan(M, w.shape[0], K)[1])
     return ops.gemm_tcgen05_prompt(x, w, out, tile_n=128)

@@ -45,7 +45,8 @@ class SwiGLU(Part):
         elif fused and linear_module.tcgen05_form(N, 2 * I, self.hidden_size, gated=True) == "weights_first":
             ops.gemm_tcgen05_mid_gated(x, self.w_gate_up, act)     # gating where the cluster's partial tiles meet
         elif fused:
-            ops.gemm_tcgen05_pair(x, self.w_gate_up, act, gated=True)  # the gating runs in the product's epilogue
+            ops.gemm_tcgen05_pair(x, self.w_gate_up, act, gated=True,  # the gating runs in the product's epilogue
+                                  splits=linear_module.pair_plan(N, 2 * I, self.hidden_size)[1])
         else:
             gate_up = ctx.scratch.get("ff.gate_up", (N, 2 * I), ctx.dtype)
             linear(x, self.w_gate_up, gate_up)

@@ -722,6 +722,58 @@ def test_tcgen05_pair_gated_epilogue(M, inter, K):
     assert np.max(np.abs(back(fused) - want)) <= 2e-2 * max(1.0, float(np.abs(want).max()))
 
 
+@pytest.mark.parametrize("M,N,K,splits", [(256, 256, 128, 2), (129, 300, 200, 3), (300, 1024, 4096, 4), (700, 6144, 1536, 3),
+                                          (1, 8, 64, 4), (520, 264, 8 * 67, 2), (256, 520, 4096, 3)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+def test_tcgen05_pair_product_with_k_split_over_a_cluster(M, N, K, splits, out_dtype):
+    """K split over 2 to 4 pairs of one cluster, partial tiles summed over distributed shared memory: ragged
+    edges in tokens, rows of W and K (a last K block that is partly beyond K, more K ranges than K blocks), in
+    both output types; equal to the 64-bit product within the bound of the unsplit kernel, the same to the bit on
+    a second run, and - with one key/row made to stand out in the LAST K range only - not blind to any range."""
+    from qwen3_b200.csrc import ops
+    g = torch.Generator(device="cuda").manual_seed(M + 3 * N + K + splits)
+    x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g, device="cuda").to(torch.bfloat16)
+    x[M // 2, K - 3] = 60.0                                   # one product that only the last K range sees
+    w[N // 3, K - 3] = 50.0
+    want = x.double() @ w.double().T
+    out = torch.full((M, N), float("nan"), dtype=DT[out_dtype], device="cuda")
+    ops.gemm_tcgen05_pair(x, w, out, splits=splits)
+    assert ops.tcgen05_status("cuda") == 0, "a wait inside the kernel gave up"
+    base, rel = (4e-5 * math.sqrt(K) * 4, 1e-6) if out_dtype == "float32" else (0.02 * math.sqrt(K), 2.0 ** -8)
+    excess = ((out.double() - want).abs() - (base + rel * want.abs())).max().item()
+    assert excess <= 0, f"an output is {excess:.3e} beyond its bound"
+    assert abs(out[M // 2, N // 3].item() - want[M // 2, N // 3].item()) <= 16.0 and want[M // 2, N // 3].item() > 2000.0
+    again = torch.full_like(out, float("nan"))
+    ops.gemm_tcgen05_pair(x, w, again, splits=splits)
+    assert torch.equal(out, again)
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tcgen05_pair(x, w, out, splits=5)
+
+
+@pytest.mark.parametrize("M,inter,K,splits", [(300, 160, 192, 2), (512, 1536, 512, 3), (77, 112, 320, 4)])
+def test_tcgen05_pair_gated_epilogue_with_k_split(M, inter, K, splits):
+    """SiLU and gating after the partial tiles have met: equal to the split product + silu_mul, bit for bit."""
+    from qwen3_b200.csrc import ops
+    g = torch.Generator(device="cuda").manual_seed(M + inter + K)
+    x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    gate = (torch.randn(inter, K, generator=g, device="cuda") * 0.2).to(torch.bfloat16)
+    up = (torch.randn(inter, K, generator=g, device="cuda") * 0.2).to(torch.bfloat16)
+    w = ops.interleave_gate_up(gate, up)
+    fused = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tcgen05_pair(x, w, fused, gated=True, splits=splits)
+    gate_up = torch.empty(M, 2 * inter, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tcgen05_pair(x, w, gate_up, splits=splits)
+    two = torch.empty_like(fused)
+    ops.silu_mul(gate_up, two, interleaved=True)
+    assert ops.tcgen05_status("cuda") == 0
+    assert torch.equal(fused, two)
+    gd = plain.round_bf16(back(x) @ back(gate).T)
+    ud = plain.round_bf16(back(x) @ back(up).T)
+    want = plain.silu_multiply(gd, ud, plain.round_bf16)
+    assert np.max(np.abs(back(fused) - want)) <= 2e-2 * max(1.0, float(np.abs(want).max()))
+
+
 @pytest.mark.parametrize("M,inter,K", [(128, 128, 64), (300, 160, 96), (2048, 1536, 512), (77, 112, 80)])
 def test_tcgen05_prompt_gated_epilogue(M, inter, K):
     """The prompt kernel with SiLU and gating in its epilogue equals product + silu_mul, bit for bit."""

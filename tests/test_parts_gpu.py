@@ -548,7 +548,8 @@ def test_rotation_of_a_part_of_the_head_stays_on_the_fused_kernels(dtype):
 
 def test_linear_takes_every_form_of_the_product():
     """`linear` chooses among the library's products by the shape: the few-row kernel, weights first (K split
-    over a cluster), tokens first on single SMs, tokens first on pairs of SMs, and the CUDA-core kernel for a
+    over a cluster), tokens first on single SMs, tokens first on pairs of SMs (with and without K split over the pairs
+    of a cluster), and the CUDA-core kernel for a
     width that is no multiple of 8.  Every choice agrees with a 64-bit product of the same operands."""
     from qwen3_b200.parts import linear as L
     from qwen3_b200.csrc import ops
@@ -564,6 +565,9 @@ def test_linear_takes_every_form_of_the_product():
             err = (out.double() - x.double() @ w.double().T).abs().max().item()
             bound = 4e-5 * np.sqrt(K) * 4 if out_dtype == torch.float32 else 0.02 * np.sqrt(K)
             assert err <= bound, (M, N, K, out_dtype, err)
-        seen.add("any_width" if K % 8 else "skinny" if M <= L.skinny_rows else L.tcgen05_form(M, N, K))
+        form = "any_width" if K % 8 else "skinny" if M <= L.skinny_rows else L.tcgen05_form(M, N, K)
+        if form == "pair" and L.pair_plan(M, N, K)[1] > 1:
+            form = "pair_k_split"
+        seen.add(form)
     assert ops.tcgen05_status("cuda") == 0
-    assert seen == {"skinny", "weights_first", "prompt128", "pair", "any_width"}, seen
+    assert seen == {"skinny", "weights_first", "prompt128", "pair", "pair_k_split", "any_width"}, seen

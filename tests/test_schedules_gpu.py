@@ -200,9 +200,9 @@ def test_8b_widths_in_unequal_batches(wide, dtype, monkeypatch):
     calls = {"pair": 0, "pair_gated": 0, "attention_tc": 0, "skinny": 0, "decode_attention": 0}
     real_pair, real_tc, real_skinny, real_dec = ops.gemm_tcgen05_pair, ops.attention_prefill_tc, ops.gemm_skinny, ops.attention_decode_fused
 
-    def pair(x, w, out, gated=False):
+    def pair(x, w, out, gated=False, splits=1):
         calls["pair_gated" if gated else "pair"] += 1
-        return real_pair(x, w, out, gated)
+        return real_pair(x, w, out, gated, splits)
 
     def tc(*a, **k):
         calls["attention_tc"] += 1
