@@ -13,22 +13,50 @@ import torch
 
 
 class Scratch:
-    """Named activation buffers that are reused from step to step (grown when needed)."""
+    """Named activation buffers that are reused from step to step (grown when needed).
 
-    def __init__(self, device):
+    With `guard` (a debugging aid for tests): every buffer has exactly the size asked for and lies between two
+    guard zones of 256 bytes filled with a pattern; `violations()` names the buffers whose zones were written."""
+
+    GUARD_BYTES, GUARD_VALUE = 256, 0xA5
+
+    def __init__(self, device, guard: bool = False):
         self.device = torch.device(device)
-        self._flat: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self.guard = guard
+        self._flat: Dict[Tuple, torch.Tensor] = {}
+        self._raw: Dict[Tuple, torch.Tensor] = {}
 
     def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         numel = 1
         for s in shape:
             numel *= int(s)
+        if self.guard:
+            return self._guarded(name, numel, dtype).view(*shape)
         key = (name, dtype)
         flat = self._flat.get(key)
         if flat is None or flat.numel() < numel:
             flat = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
             self._flat[key] = flat
         return flat[:numel].view(*shape)
+
+    def _guarded(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        key = (name, dtype, numel)
+        flat = self._flat.get(key)
+        if flat is None:
+            g = self.GUARD_BYTES
+            nbytes = numel * torch.empty((), dtype=dtype).element_size()
+            raw = torch.full((g + nbytes + g,), self.GUARD_VALUE, dtype=torch.uint8, device=self.device)
+            self._raw[key] = raw
+            flat = self._flat[key] = raw[g:g + nbytes].view(dtype)
+        return flat
+
+    def violations(self) -> list:
+        """Names (with type and size) of guarded buffers whose guard zones no longer hold the pattern."""
+        g, bad = self.GUARD_BYTES, []
+        for key, raw in self._raw.items():
+            if not (bool((raw[:g] == self.GUARD_VALUE).all()) and bool((raw[-g:] == self.GUARD_VALUE).all())):
+                bad.append(key)
+        return bad
 
 
 @dataclass

@@ -146,7 +146,7 @@ class _DecodeGraph:
         self.layout = _MetaLayout(cache, rows, rows, rows)
         self.meta = _MetaBuffer(engine.device)
         self.meta.reserve(self.layout.total)
-        self.scratch = Scratch(engine.device)
+        self.scratch = Scratch(engine.device, guard=engine.scratch.guard)
         self.ctx = context_views(cache, self.meta.dev, self.layout, rows, rows, rows, self.scratch, engine.dtype,
                                  engine.max_seq_len, is_decode=True, max_new=1, max_context=engine.max_seq_len,
                                  want_all=True)
@@ -202,7 +202,8 @@ class Engine:
     """Weights, cache, scratch and stream state of one model on one GPU."""
 
     def __init__(self, model: Model, config, max_tokens: int, max_seq_len: Optional[int] = None,
-                 n_slots: Optional[int] = None, use_graphs: bool = True):
+                 n_slots: Optional[int] = None, use_graphs: bool = True, guard_scratch: bool = False):
+        """`guard_scratch` (tests): activation buffers of exact size between guard zones; see `scratch_violations`."""
         if model.dtype is None:
             raise ValueError("the model has no weights bound")
         self.model, self.config, self.plan = model, config, model.plan
@@ -214,7 +215,7 @@ class Engine:
                              cache_from=model.cache_sources())
         self.max_seq_len = self.cache.max_seq_len
         self.vocab_size = self.plan.vocab_size
-        self.scratch = Scratch(self.device)
+        self.scratch = Scratch(self.device, guard=guard_scratch)
         self._meta = _MetaBuffer(self.device)
         # a mixer whose step depends on host values (not only on the context's device fields) opts out
         self.use_graphs = use_graphs and all(getattr(b.mixer, "graph_safe", True) for b in model.blocks)
@@ -223,10 +224,19 @@ class Engine:
         self.launches = 0          # kernels of this library launched by steps (replayed graph nodes included)
         self.last_upload_bytes = 0
 
+    def scratch_violations(self) -> list:
+        """Activation buffers (of the launched steps and of every captured decode step) that a kernel wrote beyond;
+        empty unless the engine was built with `guard_scratch` and something is wrong."""
+        bad = list(self.scratch.violations())
+        for graph in self._graphs.values():
+            bad += graph.scratch.violations()
+        return bad
+
     # -- construction
     @classmethod
     def from_folder(cls, folder: str, dtype=None, max_tokens: int = 4096, max_seq_len: Optional[int] = None,
-                    device="cuda:0", n_slots: Optional[int] = None, use_graphs: bool = True) -> "Engine":
+                    device="cuda:0", n_slots: Optional[int] = None, use_graphs: bool = True,
+                    guard_scratch: bool = False) -> "Engine":
         """Load config.json and the safetensors of `folder`; the model class is chosen by config.json."""
         config = load_config(folder)
         model = build_model(config.plan())
@@ -235,19 +245,20 @@ class Engine:
         source = open_upload(folder, model.weight_specs(), model.ignorable_names(), compute, device, model._warn_rounding)
         model.bind(source, compute, device)
         source.finish()
-        engine = cls(model, config, max_tokens, max_seq_len, n_slots, use_graphs)
+        engine = cls(model, config, max_tokens, max_seq_len, n_slots, use_graphs, guard_scratch)
         engine.weights_arena = source.arena                    # the parts' tensors are views of it
         return engine
 
     @classmethod
     def from_random(cls, config, seed: int, dtype=None, max_tokens: int = 4096, max_seq_len: Optional[int] = None,
-                    device="cuda:0", n_slots: Optional[int] = None, use_graphs: bool = True) -> "Engine":
+                    device="cuda:0", n_slots: Optional[int] = None, use_graphs: bool = True,
+                    guard_scratch: bool = False) -> "Engine":
         """Seeded random weights drawn on the device (no folder is written)."""
         model = build_model(config.plan())
         compute = DTYPES[dtype] if dtype is not None else DTYPES[getattr(config, "torch_dtype", "bfloat16")]
         weights = random_weights(model.weight_specs(), seed, dtype=compute, device=device)
         model.bind(weights, compute, device)
-        return cls(model, config, max_tokens, max_seq_len, n_slots, use_graphs)
+        return cls(model, config, max_tokens, max_seq_len, n_slots, use_graphs, guard_scratch)
 
     # -- sequences
     def new_sequence(self) -> int:

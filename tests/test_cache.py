@@ -161,3 +161,26 @@ def test_cache_need_checks():
         CacheNeed("window", 1, 16)
     with pytest.raises(ValueError):
         CacheNeed("full", 0, 16)
+
+
+def test_guarded_scratch_names_the_buffer_that_was_written_beyond():
+    """The guard zones around activation buffers (a debugging mode of the engine's scratch): a write one
+    element behind or before a buffer is found and named; buffers of other names and sizes are not."""
+    torch = pytest.importorskip("torch")
+    from qwen3_b200.engine.context import Scratch
+    scratch = Scratch("cpu", guard=True)
+    a = scratch.get("a", (3, 5), torch.float32)
+    b = scratch.get("b", (7,), torch.bfloat16)
+    assert a.shape == (3, 5) and b.shape == (7,) and scratch.get("a", (3, 5), torch.float32).data_ptr() == a.data_ptr()
+    assert scratch.get("a", (4, 5), torch.float32).data_ptr() != a.data_ptr()        # another size: a buffer of its own
+    a.fill_(1.0)
+    b.fill_(2.0)
+    assert scratch.violations() == []
+    beyond = torch.as_strided(b, (8,), (1,))                   # one element past the end
+    beyond[7] = 3.0
+    assert scratch.violations() == [("b", torch.bfloat16, 7)]
+    before = torch.as_strided(a, (1,), (1,), storage_offset=a.storage_offset() - 1)
+    before[0] = 0.0
+    assert sorted(v[0] for v in scratch.violations()) == ["a", "b"]
+    plain = Scratch("cpu")
+    assert plain.get("x", (4,), torch.float32).numel() == 4 and plain.violations() == []

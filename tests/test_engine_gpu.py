@@ -214,6 +214,61 @@ def test_step_errors_leave_the_cache_unchanged(folders):
     assert engine.cache.pages_held() == 0
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_guard_zones_and_cache_canaries_survive_every_kind_of_step(folders, name, dtype):
+    """Every activation buffer lies between guard zones and every cell of the cache starts as a canary.  After
+    whole prompts of unequal lengths, a prompt in two chunks, captured decode steps (a padded batch among them,
+    whose padding rows write to the spare page) and launched decode steps, the guard zones are intact, exactly the
+    cells of the live sequences' tokens were written, and everything else in the cache - free pages, the rows
+    behind a sequence's last token - still holds the canary."""
+    import torch
+    from qwen3_b200 import Engine, StepEntry
+    from qwen3_b200.cache import PAGE_TOKENS
+    folder, _ = folders[name]
+    cfg = tiny(name)
+    rng = np.random.default_rng(5)
+    canary = 12352.0                                           # a value bfloat16 holds exactly
+    for use_graphs in (True, False):
+        engine = Engine.from_folder(folder, dtype=dtype, max_tokens=12 * 128, use_graphs=use_graphs, guard_scratch=True)
+        for store in engine.cache.stores:
+            store.fill_(canary)
+        lengths = [70, 5, 64, 1, 33, 100, 65, 9, 17]          # nine live sequences: the captured batch is padded to 16
+        slots = [engine.new_sequence() for _ in lengths]
+        tokens = [random_tokens(rng, n, cfg["vocab_size"]) for n in lengths]
+        engine.step([StepEntry(s, t, [len(t) - 1]) for s, t in zip(slots[:4], tokens[:4])])
+        engine.step([StepEntry(s, t[:len(t) // 2], []) for s, t in zip(slots[4:], tokens[4:])])          # a prompt in two
+        engine.step([StepEntry(s, t[len(t) // 2:], [0]) for s, t in zip(slots[4:], tokens[4:])])         # chunks
+        for _ in range(3):
+            engine.step([StepEntry(s, [int(rng.integers(0, cfg["vocab_size"]))], [0]) for s in slots])
+        released_pages = {p for g in engine.cache.groups for p in g.held_pages(slots[-1])}
+        engine.release(slots.pop())                             # eight left: a batch that needs no padding
+        engine.step([StepEntry(s, [int(rng.integers(0, cfg["vocab_size"]))], [0]) for s in slots])
+        torch.cuda.synchronize()
+        assert engine.scratch_violations() == []
+        assert (len(engine._graphs) > 0) == use_graphs
+        for group, store in zip(engine.cache.groups, engine.cache.stores):
+            written = torch.zeros(store.shape[2], PAGE_TOKENS, dtype=torch.bool)
+            for s in slots:
+                pages, n = group.held_pages(s), engine.cache.length(s)
+                assert len(pages) == -(-n // PAGE_TOKENS)
+                for p in range(n):
+                    written[pages[p // PAGE_TOKENS], p % PAGE_TOKENS] = True
+            # [layers, keys/values, page, head, row, d] -> touched [page, row]: any cell that differs from the canary
+            touched = (store != canary).any(dim=-1).any(dim=3).any(dim=1).any(dim=0).cpu()
+            every = (store != canary).any(dim=-1).all(dim=3).all(dim=1).all(dim=0).cpu()
+            spare = store.shape[2] - 1
+            released = touched.clone()
+            released[:spare] &= ~written[:spare]
+            # the released sequence's pages keep its rows; apart from them nothing outside the live tokens is touched
+            live_pages = {p for s in slots for p in group.held_pages(s)}
+            stray = [(int(p), int(r)) for p, r in released[:spare].nonzero() if int(p) in live_pages]
+            assert stray == [], f"cells behind a sequence's last token were written: {stray[:5]}"
+            assert bool(every[:spare][written[:spare]].all()), "a live token's keys or values were not written in some layer or head"
+            free_touched = {int(p) for p, _ in released[:spare].nonzero()} - live_pages
+            assert free_touched <= released_pages, free_touched          # only the released sequence's own page
+
+
 def test_8b_layer_shapes_in_32_bit_match_the_plain_model():
     """One layer of the Qwen3-8B shape (hidden 4096, 32/8 heads of 128, intermediate 12288, vocabulary
     151936) in true 32-bit: whole, cut in two, and token by token agree with the float64 plain model to
