@@ -1,11 +1,13 @@
-// The C face of the host runtime (include/qwen3/cache_book.h, include/qwen3/step_pack.h) for bindings:
-// the cache book behind an opaque handle, the step packer, and the last error's text.  Every call returns
-// 0, or 1 (misuse of the cache), 2 (the cache is full), 3 (anything else); q3_host_last_error() then gives
-// the message of the calling thread's last failure.
+// The C face of the host runtime (include/qwen3/cache_book.h, step_pack.h, generation.h) for bindings:
+// the cache book behind an opaque handle, the step packer, the generation loop's decisions, and the last
+// error's text.  Every call returns 0, or 1 (misuse of the cache), 2 (the cache is full), 4 (a request that
+// cannot be generated), 3 (anything else); q3_host_last_error() then gives the message of the calling
+// thread's last failure.
 #include <cstring>
 #include <string>
 
 #include "../include/qwen3/cache_book.h"
+#include "../include/qwen3/generation.h"
 #include "../include/qwen3/step_pack.h"
 
 #define Q3_HOST_EXPORT extern "C" __attribute__((visibility("default")))
@@ -24,6 +26,9 @@ template <typename F> int guarded(F&& f) {
     } catch (const qwen3::CacheError& e) {
         g_error = e.what();
         return 1;
+    } catch (const qwen3::GenerationError& e) {
+        g_error = e.what();
+        return 4;
     } catch (const std::exception& e) {
         g_error = e.what();
         return 3;
@@ -31,6 +36,7 @@ template <typename F> int guarded(F&& f) {
 }
 
 qwen3::CacheBook* book_of(void* h) { return static_cast<qwen3::CacheBook*>(h); }
+qwen3::GenerationProgress* progress_of(void* h) { return static_cast<qwen3::GenerationProgress*>(h); }
 
 }  // namespace
 
@@ -102,4 +108,40 @@ Q3_HOST_EXPORT int q3_pack_decode_step(void* h, int rows, const int* slots, int 
         const qwen3::StepLayout lay(rows, rows, rows, b.n_groups(), b.pages_per_slot());
         qwen3::pack_decode_step(b, lay, rows, slots, n_live, token_ids, out);
     });
+}
+
+// ---- the generation loop's decisions (include/qwen3/generation.h)
+Q3_HOST_EXPORT int q3_generation_check(const int64_t* prompt_lengths, int n_requests, int64_t max_new_tokens, int64_t max_seq_len,
+                                       const int32_t* stop_token_ids, int n_stops, int64_t vocab_size) {
+    return guarded([&] { qwen3::check_requests(prompt_lengths, n_requests, max_new_tokens, max_seq_len, stop_token_ids, n_stops, vocab_size); });
+}
+// batch_of[i]: the batch (0, 1, ..) of request i; batch_size 0 = no limit beside slots and pages.
+Q3_HOST_EXPORT int q3_generation_plan_batches(const int64_t* prompt_lengths, int n_requests, int64_t max_new_tokens, int64_t n_pages,
+                                              int n_slots, int page_tokens, int batch_size, int* batch_of) {
+    return guarded([&] {
+        const std::vector<int> plan = qwen3::plan_batches(prompt_lengths, n_requests, max_new_tokens, n_pages, n_slots, page_tokens, batch_size);
+        if (!plan.empty()) std::memcpy(batch_of, plan.data(), plan.size() * sizeof(int));
+    });
+}
+Q3_HOST_EXPORT int q3_progress_create(int n_requests, int64_t max_new_tokens, const int32_t* stop_token_ids, int n_stops, void** out) {
+    return guarded([&] { *out = new qwen3::GenerationProgress(n_requests, max_new_tokens, stop_token_ids, n_stops); });
+}
+Q3_HOST_EXPORT void q3_progress_destroy(void* h) { delete progress_of(h); }
+// The tokens chosen in one step: goes_on[k] = 1 if requests[k] continues with tokens[k] fed back, else 0 and
+// reasons[k] says why it ended (1: its budget of new tokens, 2: a stop token).
+Q3_HOST_EXPORT int q3_progress_record(void* h, const int* requests, const int32_t* tokens, int n, int* goes_on, int* reasons) {
+    return guarded([&] {
+        qwen3::GenerationProgress& p = *progress_of(h);
+        for (int k = 0; k < n; ++k) {
+            goes_on[k] = p.record(requests[k], tokens[k]) ? 1 : 0;
+            reasons[k] = (int)p.reason(requests[k]);
+        }
+    });
+}
+Q3_HOST_EXPORT int q3_progress_may_run_ahead(void* h, int request) {
+    try {
+        return progress_of(h)->may_run_ahead(request) ? 1 : 0;
+    } catch (const std::exception&) {
+        return 0;
+    }
 }

@@ -14,6 +14,10 @@ Per sequence the loop is the reference's (src/generation/generator.cpp:249-323):
   the context (:163-184), stop ids must lie in the vocabulary (:186-195).
 The reference generates at batch 1 only (:79-83).
 
+The decisions - which requests may run, the batches, who goes on after a token and why the others
+ended - are the host runtime's (include/qwen3/generation.h, C++); this module binds them and drives
+the engine and the chooser with them.
+
 The loop needs of its engine only: `new_sequence()`, `release(slot)`,
 `step(entries) -> logits`, `max_seq_len`, `vocab_size`, and `cache.n_pages`,
 `cache.n_slots`, `cache.page_tokens`; and of its chooser `choose(logits, sequence_ids,
@@ -21,13 +25,68 @@ steps) -> ids`.  The tests drive it with stand-ins on the CPU.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence
+
+import numpy as np
 
 from .engine import StepEntry
 
 MAX_NEW_TOKENS = "max_new_tokens"
 STOP_TOKEN = "stop_token"
+_REASONS = {1: MAX_NEW_TOKENS, 2: STOP_TOKEN}        # qwen3::StopReason
+_lib = None
+
+
+def _host():
+    """The host runtime's generation entry points (csrc/host_runtime.cpp), bound once."""
+    global _lib
+    if _lib is None:
+        from ..cache.book import _host as load
+        lib = load()
+        p, i, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+        lib.q3_generation_check.argtypes = [p, i, i64, i64, p, i, i64]
+        lib.q3_generation_plan_batches.argtypes = [p, i, i64, i64, i, i, i, p]
+        lib.q3_progress_create.argtypes = [i, i64, p, i, ctypes.POINTER(p)]
+        lib.q3_progress_destroy.argtypes = [p]
+        lib.q3_progress_destroy.restype = None
+        lib.q3_progress_record.argtypes = [p, p, p, i, p, p]
+        lib.q3_progress_may_run_ahead.argtypes = [p, i]
+        _lib = lib
+    return _lib
+
+
+def _check(code: int) -> None:
+    if code:
+        message = _host().q3_host_last_error().decode("utf-8", "replace")
+        raise (ValueError if code == 4 else RuntimeError)(message)
+
+
+class _Progress:
+    """qwen3::GenerationProgress: what has been generated for the requests of one call, and who still runs."""
+
+    def __init__(self, n_requests: int, max_new_tokens: int, stops: Sequence[int]):
+        stops = np.asarray(sorted(stops), dtype=np.int32)
+        handle = ctypes.c_void_p()
+        _check(_host().q3_progress_create(n_requests, max_new_tokens, stops.ctypes.data, len(stops), ctypes.byref(handle)))
+        self._handle = handle
+
+    def __del__(self):
+        if getattr(self, "_handle", None) and _lib is not None:
+            _lib.q3_progress_destroy(self._handle)
+            self._handle = None
+
+    def record(self, requests: Sequence[int], tokens: Sequence[int]):
+        """(goes on?, why it ended) for each request after the token chosen for it."""
+        n = len(requests)
+        req, tok = np.asarray(requests, dtype=np.int32), np.asarray(tokens, dtype=np.int32)
+        on, why = np.empty(n, dtype=np.int32), np.empty(n, dtype=np.int32)
+        _check(_host().q3_progress_record(self._handle, req.ctypes.data, tok.ctypes.data, n, on.ctypes.data, why.ctypes.data))
+        return [bool(v) for v in on], [_REASONS.get(int(v)) for v in why]
+
+    def may_run_ahead(self, request: int) -> bool:
+        return bool(_host().q3_progress_may_run_ahead(self._handle, int(request)))
 
 
 @dataclass
@@ -40,20 +99,15 @@ class GenerationResult:
 def plan_batches(prompt_lengths: Sequence[int], max_new_tokens: int, n_pages: int, n_slots: int, page_tokens: int,
                  batch_size: Optional[int] = None) -> List[List[int]]:
     """Split request indices, in order, into batches whose worst-case page need fits the cache."""
-    batches, current, used = [], [], 0
-    for i, n in enumerate(prompt_lengths):
-        need = -(-(n + max_new_tokens) // page_tokens)
-        if need > n_pages:
-            raise ValueError(f"request {i}: {n} prompt + {max_new_tokens} new tokens need {need} pages, "
-                             f"the cache has {n_pages}")
-        full = len(current) >= n_slots or (batch_size is not None and len(current) >= batch_size)
-        if current and (full or used + need > n_pages):
-            batches.append(current)
-            current, used = [], 0
-        current.append(i)
-        used += need
-    if current:
-        batches.append(current)
+    lengths = np.asarray(list(prompt_lengths), dtype=np.int64)
+    batch_of = np.empty(len(lengths), dtype=np.int32)
+    _check(_host().q3_generation_plan_batches(lengths.ctypes.data, len(lengths), int(max_new_tokens), int(n_pages), int(n_slots),
+                                              int(page_tokens), int(batch_size or 0), batch_of.ctypes.data))
+    batches: List[List[int]] = []
+    for i, b in enumerate(batch_of):
+        if b == len(batches):
+            batches.append([])
+        batches[b].append(i)
     return batches
 
 
@@ -67,19 +121,14 @@ def generate(engine, prompts: Sequence[Sequence[int]], chooser, max_new_tokens: 
     `sequence_ids[i]` names request i to the chooser (its random stream is keyed by it); by default
     a request is named by its index, so the same prompt draws other tokens at another place of the
     list unless it is given the same name."""
-    if max_new_tokens < 0:
-        raise ValueError("max_new_tokens cannot be negative")
-    stops = set(int(s) for s in stop_token_ids)
-    for s in stops:
-        if not 0 <= s < engine.vocab_size:
-            raise ValueError(f"stop token id {s} is outside the vocabulary")
     prompts = [list(p) for p in prompts]
-    for i, p in enumerate(prompts):
-        if not p:
-            raise ValueError(f"request {i}: the prompt is empty")
-        if len(p) + max_new_tokens > engine.max_seq_len:
-            raise ValueError(f"request {i}: {len(p)} prompt tokens + {max_new_tokens} new tokens exceed the "
-                             f"context of {engine.max_seq_len}")
+    stops = sorted(set(int(t) for t in stop_token_ids))
+    lengths, stop_ids = np.asarray([len(p) for p in prompts], dtype=np.int64), np.asarray(stops, dtype=np.int64)
+    if stop_ids.size and (stop_ids.min() < -2 ** 31 or stop_ids.max() >= 2 ** 31):
+        raise ValueError("a stop token id is outside the vocabulary")
+    stop_ids = stop_ids.astype(np.int32)
+    _check(_host().q3_generation_check(lengths.ctypes.data, len(prompts), int(max_new_tokens), int(engine.max_seq_len),
+                                       stop_ids.ctypes.data, len(stops), int(engine.vocab_size)))
     if sequence_ids is None:
         names = list(range(len(prompts)))
     else:
@@ -90,10 +139,11 @@ def generate(engine, prompts: Sequence[Sequence[int]], chooser, max_new_tokens: 
     if max_new_tokens == 0 or not prompts:
         return results
     cache = engine.cache
+    progress = _Progress(len(prompts), max_new_tokens, stops)
     if hasattr(chooser, "choose_async") and getattr(engine, "device_tokens", False):
         for batch in plan_batches([len(p) for p in prompts], max_new_tokens, cache.n_pages, cache.n_slots,
                                   cache.page_tokens, batch_size):
-            _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_tokens, stops, on_token, names)
+            _run_batch_pipelined(engine, chooser, batch, prompts, results, progress, on_token, names)
         return results
     for batch in plan_batches([len(p) for p in prompts], max_new_tokens, cache.n_pages, cache.n_slots,
                               cache.page_tokens, batch_size):
@@ -107,21 +157,19 @@ def generate(engine, prompts: Sequence[Sequence[int]], chooser, max_new_tokens: 
                 chosen = chooser.choose(logits, [names[i] for i, _ in live], [step_index] * len(live))
                 if step_index % 32 == 0 and hasattr(engine, "check_kernels"):
                     engine.check_kernels()            # now and then: a kernel whose bounded wait ran out is reported
+                chosen = [int(t) for t in chosen]
+                goes_on, why = progress.record([i for i, _ in live], chosen)
                 still = []
-                for (i, slot), token in zip(live, chosen):
-                    token = int(token)
+                for (i, slot), token, on, reason in zip(live, chosen, goes_on, why):
                     results[i].token_ids.append(token)
                     if on_token is not None:
                         on_token(i, token)
-                    if token in stops:
-                        results[i].stop_reason = STOP_TOKEN
-                    elif len(results[i].token_ids) >= max_new_tokens:
-                        results[i].stop_reason = MAX_NEW_TOKENS
-                    else:
+                    if on:
                         feed[i] = [token]
                         still.append((i, slot))
-                        continue
-                    engine.release(slot)
+                    else:
+                        results[i].stop_reason = reason
+                        engine.release(slot)
                 live = still
                 step_index += 1
             if hasattr(engine, "check_kernels"):
@@ -136,7 +184,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], chooser, max_new_tokens: 
     return results
 
 
-def _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_tokens, stops, on_token, names) -> None:
+def _run_batch_pipelined(engine, chooser, batch, prompts, results, progress, on_token, names) -> None:
     """One batch with the host one step behind the device.
 
     The next step is launched before the ids of the current one have reached the host: it reads
@@ -152,7 +200,7 @@ def _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_token
         pending = chooser.choose_async(logits, [names[i] for i, _ in live], [0] * len(live))
         step_index = 0
         while live:
-            onward = [(i, slot) for i, slot in live if i not in ended and len(results[i].token_ids) + 1 < max_new_tokens]
+            onward = [(i, slot) for i, slot in live if i not in ended and progress.may_run_ahead(i)]
             upcoming = None
             if onward:
                 rows = [k for k, (i, _) in enumerate(live) if (i, _) in onward]
@@ -168,21 +216,16 @@ def _run_batch_pipelined(engine, chooser, batch, prompts, results, max_new_token
             chosen = pending.result()
             if step_index % 32 == 0 and hasattr(engine, "check_kernels"):
                 engine.check_kernels()
-            for (i, slot), token in zip(live, chosen):
-                if i in ended:
-                    continue
-                token = int(token)
+            fresh = [(i, slot, int(token)) for (i, slot), token in zip(live, chosen) if i not in ended]
+            goes_on, why = progress.record([i for i, _, _ in fresh], [t for _, _, t in fresh])
+            for (i, slot, token), on, reason in zip(fresh, goes_on, why):
                 results[i].token_ids.append(token)
                 if on_token is not None:
                     on_token(i, token)
-                if token in stops:
-                    results[i].stop_reason = STOP_TOKEN
-                elif len(results[i].token_ids) >= max_new_tokens:
-                    results[i].stop_reason = MAX_NEW_TOKENS
-                else:
-                    continue
-                ended.add(i)
-                engine.release(slot)
+                if not on:
+                    results[i].stop_reason = reason
+                    ended.add(i)
+                    engine.release(slot)
             step_index += 1
             if onward and upcoming is None:
                 onward = [(i, slot) for i, slot in onward if i not in ended]

@@ -1,4 +1,4 @@
-// A host program against the public headers (include/qwen3/cache_book.h, step_pack.h): the checks of the Python
+// A host program against the public headers (include/qwen3/cache_book.h, step_pack.h, generation.h): the checks of the Python
 // suite's cache tests, made from C++ without any binding.  Prints "ok" and exits 0, or says what failed.
 #include <cstdio>
 #include <cstdlib>
@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "qwen3/cache_book.h"
+#include "qwen3/generation.h"
 #include "qwen3/step_pack.h"
 
 #define CHECK(cond)                                                           \
@@ -150,6 +151,36 @@ int main() {
         CHECK(d[dl.token_pos] == 66 && d[dl.token_pos + 1] == 5 && d[dl.token_pos + 3] == 0);
         CHECK(d[dl.seq_slots + 2] == book.n_slots() && d[dl.tables[0] + 3 * book.pages_per_slot()] == book.n_pages());
         CHECK(d[dl.seq_start + 4] == 4 && d[dl.want_rows + 3] == 3);
+    }
+    // ---- the generation loop's decisions
+    {
+        const int64_t lengths[8] = {100, 20, 65, 64, 1, 1, 1, 200};
+        // 10 new tokens each: pages needed 2 1 2 2 1 1 1 4; a cache of 4 pages and 3 slots
+        const std::vector<int> plan = plan_batches(lengths, 8, 10, 4, 3, 64, 0);
+        const int want[8] = {0, 0, 1, 1, 2, 2, 2, 3};
+        for (int i = 0; i < 8; ++i) CHECK(plan[i] == want[i]);
+        const std::vector<int> by_two = plan_batches(lengths, 5, 1, 100, 100, 64, 2);
+        CHECK(by_two[0] == 0 && by_two[1] == 0 && by_two[2] == 1 && by_two[3] == 1 && by_two[4] == 2);
+        CHECK(throws<GenerationError>([&] { plan_batches(lengths, 8, 100, 4, 3, 64, 0); }));        // 200 + 100 tokens: 5 pages
+        const int32_t stops[2] = {7, 3};
+        check_requests(lengths, 8, 10, 210, stops, 2, 50);
+        CHECK(throws<GenerationError>([&] { check_requests(lengths, 8, 11, 210, stops, 2, 50); }));   // 200 + 11 > 210
+        CHECK(throws<GenerationError>([&] { check_requests(lengths, 8, 10, 210, stops, 2, 7); }));    // stop id 7 of 7
+        const int64_t empty[2] = {4, 0};
+        CHECK(throws<GenerationError>([&] { check_requests(empty, 2, 1, 210, stops, 0, 50); }));
+        CHECK(throws<GenerationError>([&] { check_requests(lengths, 8, -1, 210, stops, 0, 50); }));
+
+        GenerationProgress p(3, 3, stops, 2);
+        CHECK(p.running(0) && p.may_run_ahead(0));
+        CHECK(p.record(0, 5) && p.record(0, 6));                       // two of three: goes on
+        CHECK(!p.may_run_ahead(0));                                    // whatever the pending token is, it is the last
+        CHECK(!p.record(0, 9) && p.reason(0) == StopReason::MaxNewTokens && p.produced(0) == 3);
+        CHECK(!p.record(1, 3) && p.reason(1) == StopReason::StopToken && p.produced(1) == 1);      // the stop token counts
+        CHECK(p.record(2, 4) && !p.record(2, 7) && p.reason(2) == StopReason::StopToken);
+        CHECK(throws<GenerationError>([&] { p.record(1, 5); }));      // it has ended
+        CHECK(throws<GenerationError>([&] { p.record(3, 5); }));      // no such request
+        GenerationProgress none(2, 0, stops, 0);
+        CHECK(!none.running(0) && none.reason(1) == StopReason::MaxNewTokens && !none.may_run_ahead(0));
     }
     std::printf("ok\n");
     return 0;
