@@ -409,6 +409,8 @@ def main() -> int:
         for b in (1, 64):
             r = decode_run(q, engine, sampler, torch, rng, b, 2048, min(args.steps, 32), warmup, clocks)
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
+            moved = weight_bytes_per_step(cfg, layers, b) + r["cached_tokens"] * engine.cache.bytes_per_token()
+            points[f"decode_b{b}_hbm_frac"] = round(moved / (r["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
         for factor in (2, 4):
             ctx = factor * CONTEXT
             r = decode_run(q, engine, sampler, torch, rng, batch, ctx - warmup - min(args.steps, 32) - 1, min(args.steps, 32), warmup,
