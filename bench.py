@@ -455,7 +455,10 @@ def main() -> int:
         "gpu_launches": int(head["launches"]),
         "prefill": {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
                     "ms": round(prefill_ms, 3),
-                    "frac": round(flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)},
+                    "frac": round(flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
+                    # beside the burst peak: what the vendor's product keeps up for seconds under the power limit
+                    **({"frac_of_sustained": round(flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops_sustained"] * 1e12), 4)}
+                       if peaks.get("bf16_tflops_sustained") else {})},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4), "peaks": peaks["source"]},
         "points": points,
