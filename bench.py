@@ -252,7 +252,7 @@ def e2e_run(q, engine, torch, rng, batch, longest_prompt, steps, warmup, clocks=
             "host_ms": busy[0] / max(busy[1], 1) * 1e3}
 
 
-def products_against_the_vendor_library(torch, cfg, copies=6, repeats=21):
+def products_against_the_vendor_library(torch, cfg, copies=6, repeats=21, token_counts=(129, 256, 512, 1024, 2048, 4096)):
     """Microseconds of Y = X . W^T for the q/k/v, output, gate/up and down projections of one layer, per token
     count: `ours` through parts.linear (the kernels the engine runs), `vendor` through torch.mm (cuBLAS).  Each
     is a CUDA graph of `copies` products over different weights (more than the L2 holds), the median of
@@ -283,7 +283,7 @@ def products_against_the_vendor_library(torch, cfg, copies=6, repeats=21):
         return statistics.median(times) / copies * 1e3
 
     out = {"config": {"hidden": H, "intermediate": I, "copies": copies, "repeats": repeats}, "rows": []}
-    for M in (129, 256, 512, 1024, 2048, 4096):
+    for M in token_counts:
         sums = [0.0, 0.0]
         for name, N, K in shapes:
             ws = [torch.randn(N, K, device="cuda").to(torch.bfloat16) for _ in range(copies)]
@@ -351,6 +351,8 @@ def main() -> int:
     ap.add_argument("--products", action="store_true",
                     help="instead of the benchmark: the four projections of a layer at 129..4,096 tokens, this library's "
                          "kernels against the vendor library's (torch.mm), both replayed from CUDA graphs over rotating weights")
+    ap.add_argument("--tokens", type=int, action="append", default=None,
+                    help="with --products: only this token count (may be given several times); keeps a profiler's capture small")
     ap.add_argument("--kernels", action="store_true",
                     help="instead of the benchmark: time every kernel of one decode step and of one 2,048-token prompt step "
                          "with CUDA events (steps launched afresh, not replayed) and print the sums per entry point")
@@ -374,7 +376,8 @@ def main() -> int:
     cfg, CONTEXT, shape_batch = SHAPES[args.shape]
     if args.products:
         torch.cuda.set_device(0)
-        print(json.dumps(products_against_the_vendor_library(torch, cfg)))
+        counts = tuple(args.tokens) if args.tokens else (129, 256, 512, 1024, 2048, 4096)
+        print(json.dumps(products_against_the_vendor_library(torch, cfg, token_counts=counts)))
         return 0
     CONTEXT = args.context or CONTEXT
     layers = args.layers or cfg["num_hidden_layers"]
