@@ -27,19 +27,28 @@ class KernelError(RuntimeError):
     """A kernel refused its arguments or its launch failed."""
 
 
-_pdl = os.environ.get("QWEN3_B200_PDL", "0") == "1"
+# Programmatic dependent launch: a kernel launched with it may start (set up its barriers and tensor memory, fetch
+# weights) while the kernel before it on the stream drains, and waits for that kernel's results only where it
+# first needs them.  By default the sources named here launch their kernels that way: measured on whole decode
+# steps of an 8B-sized model, the TMA + tcgen05 products gain 2.5-5 % at batches of 16 to 64 (4.92 -> 4.74 ms a
+# step at batch 16), while the few-row product and the small kernels around it lose (batch 8: chains of waiting
+# blocks take the room that a kernel's own later waves need).  QWEN3_B200_PDL=1 / =0 turns it on / off for all.
+PDL_SOURCES = ("gemm_tcgen05.cu",)
+_pdl_override = {"1": True, "0": False}.get(os.environ.get("QWEN3_B200_PDL", ""))
 _libs = {}
 
 
-def set_pdl(on: bool) -> None:
-    """Programmatic dependent launch for every kernel of the library: a kernel may start (and
-    fetch weights) while the one before it on the stream drains.  Off by default (measured
-    slower for whole decode steps, where chains of waiting kernels take the SMs' room);
-    the environment variable QWEN3_B200_PDL=1 turns it on."""
-    global _pdl
-    _pdl = bool(on)
-    for lib in _libs.values():
-        lib.q3_set_pdl(int(_pdl))
+def _pdl_for(source: str) -> bool:
+    return _pdl_override if _pdl_override is not None else source in PDL_SOURCES
+
+
+def set_pdl(on) -> None:
+    """Programmatic dependent launch for every kernel of the library (True / False), or back to the default
+    (None): on for the sources in `PDL_SOURCES` only."""
+    global _pdl_override
+    _pdl_override = None if on is None else bool(on)
+    for (source, _), lib in _libs.items():
+        lib.q3_set_pdl(int(_pdl_for(source)))
 
 
 class KernelTimer:
@@ -104,7 +113,7 @@ def _fn_untimed(source: str, name: str, argtypes, defines=()):
             _libs[(source, tuple(defines))] = lib
             lib.q3_set_pdl.argtypes = [c_int]
             lib.q3_set_pdl.restype = None
-            lib.q3_set_pdl(int(_pdl))
+            lib.q3_set_pdl(int(_pdl_for(source)))
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
