@@ -149,7 +149,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     tokenizer_path = os.path.join(model_dir or "", "tokenizer.json")
     if not os.path.isfile(tokenizer_path):
         ap.error("no tokenizer.json in the model folder: give prompts as token ids with --tokens")
-    from .chat_template import apply_chat_template, split_thinking
+    from .chat_template import apply_chat_template, parse_answer, split_thinking
     from .tokenizer import Tokenizer
     tokenizer = Tokenizer.load(tokenizer_path)
     if tokenizer.vocab_size > plan.vocab_size:
@@ -184,16 +184,31 @@ def main(argv: Optional[List[str]] = None) -> int:
             print("[the conversation no longer fits the context; use /clear]")
             history.pop()
             continue
-        # like the reference, every turn prefills the whole history into a fresh sequence (:992)
-        result = q.generate_token_ids(engine, [ids], sampling,
-                                      q.GenerationOptions(min(args.max_new_tokens, room), stops))[0]
+        # like the reference, every turn prefills the whole history into a fresh sequence (:992); a turn that
+        # fails, or that ends inside the reasoning block, is taken back so that user and assistant still alternate
+        # (:1036-1055, :1086-1100)
+        try:
+            result = q.generate_token_ids(engine, [ids], sampling,
+                                          q.GenerationOptions(min(args.max_new_tokens, room), stops))[0]
+        except Exception as error:            # the conversation goes on without this turn
+            history.pop()
+            print(f"[generation failed: {error}]", file=sys.stderr)
+            continue
         out = result.token_ids[:-1] if result.stop_reason == q.STOP_TOKEN else result.token_ids
         text = tokenizer.decode(out)
-        thought, answer = split_thinking(text)
+        answer, _, complete = parse_answer(text)
+        thought, _ = split_thinking(text)
+        if not complete:
+            print(f"[thinking]\n{thought}" if args.show_thinking else "[the reasoning is hidden]")
+            print("[the model stopped before it gave an answer; this turn is not kept in the conversation]")
+            history.pop()
+            continue
         if thought and args.show_thinking:
             print(f"[thinking]\n{thought}\n[answer]")
         print(answer)
         history.append(("assistant", answer))
+        if result.stop_reason == q.MAX_NEW_TOKENS:
+            print("[the answer was cut at --max-new-tokens]")
     return 0
 
 

@@ -39,11 +39,26 @@ def apply_chat_template(messages: List[Tuple[str, str]], add_generation_prompt: 
     return "".join(parts)
 
 
+def parse_answer(text: str) -> Tuple[str, bool, bool]:
+    """(final answer, a thinking block was seen, the thinking block was closed) of a raw response, as the reference
+    reads it (apps/qwen3_chat.cpp:593-643): everything after the LAST </think>, with the line breaks right behind
+    the tag dropped; an opening tag without a closing one means the model stopped while it was still thinking - no
+    final answer; a response without either tag is the answer itself."""
+    end = text.rfind("</think>")
+    if end >= 0:
+        return text[end + len("</think>"):].lstrip("\n\r"), True, True
+    if "<think>" in text:
+        return "", True, False
+    return text, False, True
+
+
 def split_thinking(text: str) -> Tuple[str, str]:
-    """(thinking, answer) of a response that may open with a <think>...</think> block
-    (apps/qwen3_chat.cpp:593-643)."""
-    start, end = text.find("<think>"), text.find("</think>")
-    if end < 0:
-        return ("", text) if start < 0 else (text[start + 7:].strip(), "")
-    begin = start + 7 if 0 <= start < end else 0
-    return text[begin:end].strip(), text[end + 8:].lstrip("\n")
+    """(thinking, answer) of a response that may open with a <think>...</think> block: `parse_answer`'s final
+    answer beside the text of the thinking block (for printing it apart from the answer)."""
+    answer, saw, closed = parse_answer(text)
+    if not saw:
+        return "", answer
+    start = text.find("<think>")
+    begin = start + len("<think>") if start >= 0 else 0
+    end = text.rfind("</think>") if closed else len(text)
+    return text[begin:end].strip(), answer

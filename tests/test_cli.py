@@ -4,7 +4,7 @@ import json
 import pytest
 
 from qwen3_b200.cli.chat import build_parser, parse_ids
-from qwen3_b200.cli.chat_template import apply_chat_template, split_thinking
+from qwen3_b200.cli.chat_template import apply_chat_template, parse_answer, split_thinking
 from qwen3_b200.cli.tokenizer import Tokenizer, bytes_to_unicode
 
 PATTERN = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+"
@@ -26,6 +26,13 @@ def test_chat_template_strings():
     assert split_thinking("<think>\nhm\n</think>\n\nyes") == ("hm", "yes")
     assert split_thinking("plain") == ("", "plain")
     assert split_thinking("hm</think>\n\nyes") == ("hm", "yes")
+    # the reference's reading of a raw response (apps/qwen3_chat.cpp:593-643)
+    assert parse_answer("<think>a</think>\n\r\nyes\n") == ("yes\n", True, True)
+    assert parse_answer("<think>a</think>b</think>\nc") == ("c", True, True)          # the last closing tag counts
+    assert parse_answer("<think>still going") == ("", True, False)                    # stopped inside the reasoning
+    assert parse_answer("no tags") == ("no tags", False, True)
+    assert split_thinking("<think>still going") == ("still going", "")
+    assert split_thinking("<think>a</think>b</think>\nc") == ("a</think>b", "c")
 
 
 def make_tokenizer(tmp_path):

@@ -132,3 +132,26 @@ def test_command_line_with_raw_token_ids(folders):
     for p, line in zip(prompts, lines):
         ids = [int(t) for t in line.split("#")[0].strip().split(",")]
         assert ids == plain.generate_greedy(cfg, weights, p, 6, stops)
+
+
+def test_chat_loop_with_a_tokenizer(tmp_path):
+    """The chat loop end to end on a tiny random model with a tokenizer of its own: template, encoding, generation
+    limited to the tokenizer's ids, decoding and the turn handling.  The same message gives the same answer after
+    /clear (every turn prefills the whole history into a fresh sequence), an answer cut by --max-new-tokens says
+    so (the model's stop ids lie outside the tokenizer's ids here, so no answer ends by itself), and /exit leaves
+    with 0."""
+    from test_cli import make_tokenizer
+    folder, _ = make_folder(tmp_path, tiny("C"), seed=5)
+    make_tokenizer(tmp_path)
+    os.replace(os.path.join(str(tmp_path), "tokenizer.json"), os.path.join(folder, "tokenizer.json"))
+    script = "hello world\n/clear\nhello world\n/think off\nhello\n/help\n/exit\n"
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "qwen3_chat"), folder, "--greedy", "--dtype", "float32",
+                          "--max-new-tokens", "4", "--max-context", "128"], input=script, capture_output=True, text=True,
+                         timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    turns = out.stdout.split("[the answer was cut at --max-new-tokens]")
+    assert len(turns) == 4, out.stdout                           # three answers, each cut after 4 tokens
+    first = turns[0].split("> ", 1)[1]
+    second = turns[1].split("> > ", 1)[1]                         # the prompts of /clear and of the next message
+    assert first == second and first.strip() != ""
+    assert "/think on" in out.stdout                              # /help printed the commands
