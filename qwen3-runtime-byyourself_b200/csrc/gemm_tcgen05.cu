@@ -474,6 +474,197 @@ gemm_tcgen05_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
 //   acc_empty[b]  in the leader: the eight drain warps of both blocks arrive there
 // Only the leader issues tcgen05.mma.  Every wait is bounded as above, and both blocks meet at a
 // cluster barrier before either leaves (the peer's shared memory and barriers are in use until then).
+// The epilogue of the q/k/v product for prompts: what qkv_prepare (attention.cu) does to the product's output, done
+// on the accumulator instead, so that the [tokens, (nq + 2 nkv) d] matrix is never written and read back.  A thread
+// of the epilogue owns one token and, in a tile of 256 columns, 256 / d whole heads of it: the sum of squares of
+// a head, its normalisation (round(round(x * inv) * w), as the reference's per-head RMSNorm), the rotation of
+// the pairs (i, i + d/2) by the token's position and the write - q to its matrix, k and v to the token's place
+// in the pages - are all the thread's own.  The accumulator is rounded to bfloat16 first, as the product's
+// output would have been.  Head sizes 64, 128 and 256 (whole heads in a tile, halves of whole 32-column chunks).
+// What it costs: a thread's token has its own row of the rotation tables and its own rows of q and of the pages, so
+// every load and store of a warp touches 32 lines, and the four warps of a block share one path to memory: a tile's
+// epilogue takes about 12 us where the plain one takes 3.  Under the next tile's K steps (21 us at K = 4,096) that is
+// hidden, for a pair's last tile it is not: at 8,192 tokens the fused product takes 321-338 us against 381-412 for
+// product + qkv_prepare, at 2,048 tokens 83.5 against 86, at 512 tokens (one tile a pair) 41 against 34 - so it
+// is used from 2,048 tokens on (parts/attention.py).
+
+struct QkvEpilogue {
+    bf16* q_out;                   // [tokens, nq * d]
+    bf16* k_pages;                 // [pages, nkv, Q3_PAGE_TOKENS, d]
+    bf16* v_pages;
+    const float* q_norm_w;         // [d] or null
+    const float* k_norm_w;
+    const float* cos_tab;          // [positions, d / 2] or null
+    const float* sin_tab;
+    const int* token_seq;          // [tokens]: row of the page table
+    const int* token_pos;          // [tokens]: position in the sequence
+    const int* page_table;         // [sequences, pages_per_seq]
+    int pages_per_seq, nq, nkv, d, write_kv;
+    float eps;
+};
+
+__device__ __forceinline__ void store_bf16x8(bf16* p, const float (&v)[8]) {
+    uint4 o;
+    __nv_bfloat162 t;
+    t = __floats2bfloat162_rn(v[0], v[1]); o.x = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(v[2], v[3]); o.y = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(v[4], v[5]); o.z = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(v[6], v[7]); o.w = *reinterpret_cast<uint32_t*>(&t);
+    *reinterpret_cast<uint4*>(p) = o;
+}
+__device__ __forceinline__ void load_f32x8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+// One head of one token: D accumulator columns from `acc` on.  D = 64 or 128: the whole head is taken into
+// registers with one wait, so the sum of squares, the normalisation and the rotation need no second pass over
+// tensor memory.
+template <int D>
+__device__ __forceinline__ void qkv_head_in_registers(uint32_t acc, bool live, bf16* dst, const float* nw, float eps,
+                                                      const float* cs_row, const float* sn_row) {
+    constexpr int HALF = D / 2, CHUNKS = D / 32;
+    uint32_t r[CHUNKS][32];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) tc_ld32(acc + (uint32_t)(c * 32), r[c]);
+    tc_wait_ld();
+    if (!live) return;
+    float inv = 1.0f;
+    if (nw != nullptr) {
+        float sq = 0.0f;
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float v = round_to<bf16>(__uint_as_float(r[c][j]));
+                sq += v * v;
+            }
+        inv = rsqrtf(sq / (float)D + eps);
+    }
+#pragma unroll
+    for (int i0 = 0; i0 < HALF; i0 += 8) {
+        float x[8], y[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            x[i] = round_to<bf16>(__uint_as_float(r[(i0 + i) / 32][(i0 + i) % 32]));
+            y[i] = round_to<bf16>(__uint_as_float(r[(HALF + i0 + i) / 32][(HALF + i0 + i) % 32]));
+        }
+        if (nw != nullptr) {
+            float wx[8], wy[8];
+            load_f32x8(nw + i0, wx);
+            load_f32x8(nw + HALF + i0, wy);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                x[i] = round_to<bf16>(round_to<bf16>(x[i] * inv) * wx[i]);
+                y[i] = round_to<bf16>(round_to<bf16>(y[i] * inv) * wy[i]);
+            }
+        }
+        if (cs_row != nullptr) {
+            float cs[8], sn[8];
+            load_f32x8(cs_row + i0, cs);
+            load_f32x8(sn_row + i0, sn);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float xr = x[i] * cs[i] - y[i] * sn[i], yr = y[i] * cs[i] + x[i] * sn[i];
+                x[i] = xr;
+                y[i] = yr;
+            }
+        }
+        store_bf16x8(dst + i0, x);
+        store_bf16x8(dst + HALF + i0, y);
+    }
+}
+
+// The same for any head size that is a multiple of 64 (here: 256), in two passes over tensor memory.
+__device__ __forceinline__ void qkv_head_two_passes(uint32_t acc, int d, bool live, bf16* dst, const float* nw, float eps,
+                                                    const float* cs_row, const float* sn_row) {
+    const int half = d >> 1;
+    float inv = 1.0f;
+    if (nw != nullptr) {
+        float sq = 0.0f;
+#pragma unroll 1
+        for (int c = 0; c < d; c += 32) {
+            uint32_t r[32];
+            tc_ld32(acc + (uint32_t)c, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float v = round_to<bf16>(__uint_as_float(r[j]));
+                sq += v * v;
+            }
+        }
+        inv = rsqrtf(sq / (float)d + eps);
+    }
+#pragma unroll 1
+    for (int c = 0; c < half; c += 32) {
+        uint32_t a[32], b[32];                             // columns c .. c + 31 of both halves of the head
+        tc_ld32(acc + (uint32_t)c, a);
+        tc_ld32(acc + (uint32_t)(half + c), b);
+        tc_wait_ld();
+        if (!live) continue;
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            float x[8], y[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                x[i] = round_to<bf16>(__uint_as_float(a[j + i]));
+                y[i] = round_to<bf16>(__uint_as_float(b[j + i]));
+            }
+            if (nw != nullptr) {
+                float wx[8], wy[8];
+                load_f32x8(nw + c + j, wx);
+                load_f32x8(nw + half + c + j, wy);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    x[i] = round_to<bf16>(round_to<bf16>(x[i] * inv) * wx[i]);
+                    y[i] = round_to<bf16>(round_to<bf16>(y[i] * inv) * wy[i]);
+                }
+            }
+            if (cs_row != nullptr) {
+                float cs[8], sn[8];
+                load_f32x8(cs_row + c + j, cs);
+                load_f32x8(sn_row + c + j, sn);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float xr = x[i] * cs[i] - y[i] * sn[i], yr = y[i] * cs[i] + x[i] * sn[i];
+                    x[i] = xr;
+                    y[i] = yr;
+                }
+            }
+            store_bf16x8(dst + c + j, x);
+            store_bf16x8(dst + half + c + j, y);
+        }
+    }
+}
+
+// `acc`: the thread's row of the tile's accumulator in tensor memory; token `m`, tile columns n0 .. n0 + 255.
+__device__ __forceinline__ void qkv_tile_epilogue(uint32_t acc, int m, bool token_valid, int n0, int N, const QkvEpilogue& e) {
+    const int d = e.d, half = d >> 1;
+    int pos = 0;
+    int64_t page = 0;
+    if (token_valid) {
+        pos = e.token_pos[m];
+        if (e.write_kv) page = e.page_table[(int64_t)e.token_seq[m] * e.pages_per_seq + pos / Q3_PAGE_TOKENS];
+    }
+    for (int h0 = 0; h0 < 256 && n0 + h0 < N; h0 += d) {       // the same heads for every thread of the warp
+        const int head = (n0 + h0) / d;
+        const bool is_q = head < e.nq, is_v = head >= e.nq + e.nkv;
+        const float* nw = is_q ? e.q_norm_w : (is_v ? nullptr : e.k_norm_w);
+        const bool live = token_valid && (is_q || e.write_kv);
+        const bool rotate = e.cos_tab != nullptr && !is_v;
+        bf16* dst = nullptr;
+        if (live)
+            dst = is_q ? e.q_out + ((int64_t)m * e.nq + head) * d
+                       : (is_v ? e.v_pages : e.k_pages) +
+                             ((page * e.nkv + (head - e.nq) % e.nkv) * Q3_PAGE_TOKENS + pos % Q3_PAGE_TOKENS) * d;
+        const float* cs_row = rotate ? e.cos_tab + (int64_t)pos * half : nullptr;
+        const float* sn_row = rotate ? e.sin_tab + (int64_t)pos * half : nullptr;
+        if (d == 128) qkv_head_in_registers<128>(acc + (uint32_t)h0, live, dst, nw, e.eps, cs_row, sn_row);
+        else if (d == 64) qkv_head_in_registers<64>(acc + (uint32_t)h0, live, dst, nw, e.eps, cs_row, sn_row);
+        else qkv_head_two_passes(acc + (uint32_t)h0, d, live, dst, nw, e.eps, cs_row, sn_row);
+    }
+}
+
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_in_leader, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar_in_leader), "r"(x), "r"(y) : "memory");
@@ -495,10 +686,10 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
-template <int STAGES, bool GATED, typename OutT>
+template <int STAGES, bool GATED, typename OutT, bool QKV = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                         OutT* __restrict__ Y, int M, int N, int K, int* __restrict__ status) {
+                         OutT* __restrict__ Y, int M, int N, int K, int* __restrict__ status, const QkvEpilogue qkv) {
     extern __shared__ unsigned char smem_raw[];
     constexpr int BN = 256, PAIR_M = 2 * BM;
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -597,13 +788,17 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             }
             tc_fence_after();
             const int m = m0 + lane_base + lane;
-            OutT* row = Y + (int64_t)m * (GATED ? (N >> 1) : N) + (GATED ? (n0 >> 1) : n0);
+            if constexpr (QKV) {
+                qkv_tile_epilogue(tmem_base + ((uint32_t)lane_base << 16) + buf * BN, m, m < M, n0, N, qkv);
+            } else {
+                OutT* row = Y + (int64_t)m * (GATED ? (N >> 1) : N) + (GATED ? (n0 >> 1) : n0);
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t r[32];
-                tc_ld32(tmem_base + ((uint32_t)lane_base << 16) + buf * BN + (uint32_t)c, r);
-                tc_wait_ld();
-                store_chunk32<GATED, OutT>(r, row, c, n0, m < M, N, vec_ok);
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tc_ld32(tmem_base + ((uint32_t)lane_base << 16) + buf * BN + (uint32_t)c, r);
+                    tc_wait_ld();
+                    store_chunk32<GATED, OutT>(r, row, c, n0, m < M, N, vec_ok);
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -852,20 +1047,21 @@ int launch_prompt(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, in
                           map_x, map_w, Y, M, N, K, status);
 }
 
-template <int STAGES, bool GATED, typename OutT>
-int launch_pair(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int* status, cudaStream_t stream) {
+template <int STAGES, bool GATED, typename OutT, bool QKV = false>
+int launch_pair(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int* status, cudaStream_t stream,
+                const QkvEpilogue& qkv = QkvEpilogue{}) {
     constexpr int SMEM = STAGES * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256;
     static Q3PerDevice configured;
     {
-        cudaError_t e = q3_allow_shared_memory(gemm_tcgen05_pair_kernel<STAGES, GATED, OutT>, SMEM, configured);
+        cudaError_t e = q3_allow_shared_memory(gemm_tcgen05_pair_kernel<STAGES, GATED, OutT, QKV>, SMEM, configured);
         if (e != cudaSuccess) return (int)e;
     }
     CUtensorMap map_x, map_w;
     if (!make_map(&map_x, X, M, K, BM) || !make_map(&map_w, W, N, K, 128)) return Q3_ERR_BAD_SIZE;
     const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
     const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
-    return (int)q3_launch_cluster(gemm_tcgen05_pair_kernel<STAGES, GATED, OutT>, dim3(2 * pairs), dim3(THREADS), (size_t)SMEM,
-                                  stream, dim3(2, 1, 1), map_x, map_w, Y, M, N, K, status);
+    return (int)q3_launch_cluster(gemm_tcgen05_pair_kernel<STAGES, GATED, OutT, QKV>, dim3(2 * pairs), dim3(THREADS), (size_t)SMEM,
+                                  stream, dim3(2, 1, 1), map_x, map_w, Y, M, N, K, status, qkv);
 }
 
 template <int STAGES, bool GATED, typename OutT>
@@ -956,6 +1152,31 @@ Q3_EXPORT int q3_gemm_tcgen05_pair_bf16(const void* X, const void* W, void* Y, i
 
 // Pairs of SMs that run at once when K is split over `splits` pairs of a cluster (0: the device cannot place it).
 Q3_EXPORT int q3_gemm_tcgen05_pair_capacity(int splits) { return pair_capacity(splits); }
+
+// The q/k/v product of a prompt step with qkv_prepare's work in its epilogue (see QkvEpilogue): W [(nq + 2 nkv) d, K]
+// holds the q, k and v rows one after the other; q goes to q_out [M, nq d], k and v (if write_kv) to the pages.
+// Head sizes 64, 128 and 256; the rotation tables cover the whole head ([positions, d / 2]) or are null.
+Q3_EXPORT int q3_gemm_tcgen05_pair_qkv_bf16(const void* X, const void* W, int M, int K, void* q_out, void* k_pages, void* v_pages,
+                                            const float* q_norm_w, const float* k_norm_w, const float* cos_tab,
+                                            const float* sin_tab, float eps, const int* token_seq, const int* token_pos,
+                                            const int* page_table, int pages_per_seq, int nq, int nkv, int d, int write_kv,
+                                            int* status, void* stream_) {
+    if (M <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || nq <= 0 || nkv <= 0 || (d != 64 && d != 128 && d != 256)) return Q3_ERR_BAD_SIZE;
+    if ((cos_tab == nullptr) != (sin_tab == nullptr) || (q_norm_w == nullptr) != (k_norm_w == nullptr)) return Q3_ERR_BAD_SIZE;
+    if (!aligned16(X) || !aligned16(W) || !aligned16(q_out) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(q_norm_w) ||
+        !aligned16(k_norm_w) || !aligned16(cos_tab) || !aligned16(sin_tab))
+        return Q3_ERR_MISALIGNED;
+    const int64_t N = (int64_t)(nq + 2 * nkv) * d;
+    if (N > 0x7fffffff) return Q3_ERR_TOO_LARGE;
+    QkvEpilogue e;
+    e.q_out = (bf16*)q_out; e.k_pages = (bf16*)k_pages; e.v_pages = (bf16*)v_pages;
+    e.q_norm_w = q_norm_w; e.k_norm_w = k_norm_w; e.cos_tab = cos_tab; e.sin_tab = sin_tab;
+    e.token_seq = token_seq; e.token_pos = token_pos; e.page_table = page_table;
+    e.pages_per_seq = pages_per_seq; e.nq = nq; e.nkv = nkv; e.d = d; e.write_kv = write_kv; e.eps = eps;
+    return launch_pair<6, false, bf16, true>((const bf16*)X, (const bf16*)W, (bf16*)nullptr, M, (int)N, K, status,
+                                             (cudaStream_t)stream_, e);
+}
 
 // W [N, K] holds gate and up rows interleaved in blocks of eight; Y [M, N/2] = round(silu(g)) * u, bfloat16.
 Q3_EXPORT int q3_gemm_tcgen05_prompt_gated_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int* status,

@@ -604,6 +604,35 @@ def gemm_tcgen05_pair_capacity(splits: int) -> int:
     return int(fn(int(splits)))
 
 
+PAIR_QKV_HEAD_DIMS = (64, 128, 256)
+
+
+def gemm_tcgen05_pair_qkv(x: torch.Tensor, w: torch.Tensor, q_out, k_pages, v_pages, q_norm_w, k_norm_w, cos, sin, eps,
+                          token_seq, token_pos, page_table, n_tokens: int, nq: int, nkv: int, d: int,
+                          write_kv: bool = True) -> None:
+    """The q/k/v product of a prompt step on pairs of SMs with `qkv_prepare`'s work in its epilogue: per-head
+    RMSNorm of q and k (weights may be None), rotation of the whole head (tables [positions, d/2], may be None),
+    q into q_out [n_tokens, nq*d], k and v into the pages at the tokens' positions (`write_kv`); the product's
+    own output is never stored.  w [(nq + 2 nkv) d, K] holds the q, k and v rows one after the other.  bfloat16,
+    head sizes 64, 128 and 256."""
+    M, K = x.shape
+    if x.dtype != torch.bfloat16 or M != n_tokens or w.shape != ((nq + 2 * nkv) * d, K) or K % 8 != 0 or d not in PAIR_QKV_HEAD_DIMS:
+        raise KernelError(f"gemm_tcgen05_pair_qkv: shapes {tuple(x.shape)} x {tuple(w.shape)}^T for {nq}+2*{nkv} heads of {d}")
+    if q_out.shape != (n_tokens, nq * d) or (q_norm_w is None) != (k_norm_w is None) or (cos is None) != (sin is None):
+        raise KernelError("gemm_tcgen05_pair_qkv: q_out, norm weights or tables do not fit")
+    if cos is not None and _rotary_dim(cos, sin, d) != d:
+        raise KernelError("gemm_tcgen05_pair_qkv rotates the whole head only")
+    fn = _fn("gemm_tcgen05.cu", "q3_gemm_tcgen05_pair_qkv_bf16",
+             [c_void_p, c_void_p, c_int, c_int] + [c_void_p] * 7 + [c_float] + [c_void_p] * 3 + [c_int] * 5 + [c_void_p, c_void_p])
+    _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), M, K, _dev(q_out, "q_out", torch.bfloat16),
+              _dev(k_pages, "k_pages", torch.bfloat16), _dev(v_pages, "v_pages", torch.bfloat16),
+              _ptr(q_norm_w, "q_norm_w", torch.float32), _ptr(k_norm_w, "k_norm_w", torch.float32),
+              _ptr(cos, "cos", torch.float32), _ptr(sin, "sin", torch.float32), float(eps),
+              _dev(token_seq, "token_seq", torch.int32), _dev(token_pos, "token_pos", torch.int32),
+              _dev(page_table, "page_table", torch.int32), page_table.shape[-1], nq, nkv, d, int(bool(write_kv)),
+              _status_word(x.device).data_ptr(), _stream()), "gemm_tcgen05_pair_qkv")
+
+
 def gemm_tcgen05_prompt_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[M, N/2] = round(silu(g)) * u for many rows; `w` [N, K] holds the gate and up rows interleaved in
     blocks of eight (`interleave_gate_up`); the gating runs in the product's epilogue."""

@@ -111,6 +111,12 @@ int q3_gemm_tcgen05_mid_splits(int N, int K, int M);
 int q3_gemm_tcgen05_prompt_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int tile_n, int* status,
                                 void* stream);
 int q3_gemm_tcgen05_prompt_gated_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int* status, void* stream);
+/* the q/k/v product of a prompt step with q3_qkv_prepare's work in its epilogue: W [(nq + 2 nkv) d, K]; q to q_out
+   [M, nq d], k and v (write_kv) to the pages; d 64, 128 or 256; norm weights and whole-head tables may be null */
+int q3_gemm_tcgen05_pair_qkv_bf16(const void* X, const void* W, int M, int K, void* q_out, void* k_pages, void* v_pages,
+                                  const float* q_norm_w, const float* k_norm_w, const float* cos_tab, const float* sin_tab, float eps,
+                                  const int* token_seq, const int* token_pos, const int* page_table, int pages_per_seq, int nq,
+                                  int nkv, int d, int write_kv, int* status, void* stream);
 /* splits 1..4: K split over that many pairs of SMs of one cluster (1: persistent pairs, no split) */
 int q3_gemm_tcgen05_pair_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int gated, int splits,
                               int* status, void* stream);

@@ -28,6 +28,9 @@ DECODE_KERNELS = []
 # Kernels that take the projection output as it is and do norm, rotation, cache write and attention of a decode
 # step in one launch: fn(part, qkv, cache, out, ctx, table, q_norm_w, k_norm_w, eps, cos, sin) -> bool
 FUSED_DECODE_KERNELS = []
+# Kernels that do the q/k/v product of a prompt step themselves, with norm, rotation and cache write in its
+# epilogue: fn(part, x, cache, q, ctx, table, q_norm_w, k_norm_w, eps, cos, sin) -> bool (q is filled, the pages written)
+FUSED_PROJECTION_KERNELS = []
 
 
 class GQAAttention(Part):
@@ -73,8 +76,6 @@ class GQAAttention(Part):
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         N = ctx.n_tokens
         table = ctx.page_tables[cache.group]
-        qkv = ctx.scratch.get("attn.qkv", (N, (nq + 2 * nkv) * d), ctx.dtype)
-        linear(x, self.w_qkv, qkv)
         attn = ctx.scratch.get("attn.ctx", (N, nq * d), ctx.dtype)
         out = ctx.scratch.get("mixer.out", (N, self.hidden_size), ctx.dtype)
         norm_eps = self.q_norm.eps if self.q_norm is not None else 0.0
@@ -85,6 +86,14 @@ class GQAAttention(Part):
         if tables and self.position is not None:
             self.position.prepare(ctx.max_positions, ctx.device)
             cos, sin = self.position.cos, self.position.sin
+        if tables and not ctx.is_decode and ctx.dtype == torch.bfloat16:
+            q = ctx.scratch.get("attn.q", (N, nq * d), ctx.dtype)
+            for kernel in FUSED_PROJECTION_KERNELS:
+                if kernel(self, x, cache, q, ctx, table, qw, kw, norm_eps, cos, sin):
+                    self.attend(q, cache, attn, ctx, table)
+                    return linear(attn, self.w_o, out)
+        qkv = ctx.scratch.get("attn.qkv", (N, (nq + 2 * nkv) * d), ctx.dtype)
+        linear(x, self.w_qkv, qkv)
         if tables and ctx.is_decode and ctx.dtype == torch.bfloat16:
             for kernel in FUSED_DECODE_KERNELS:
                 if kernel(self, qkv, cache, attn, ctx, table, qw, kw, norm_eps, cos, sin):
@@ -149,6 +158,24 @@ def _decode_fused_kernel(part, qkv, cache, out, ctx, table, q_norm_w, k_norm_w, 
     return True
 
 
+def _projection_pair_kernel(part, x, cache, q, ctx, table, q_norm_w, k_norm_w, eps, cos, sin) -> bool:
+    """The q/k/v product on pairs of SMs with norm, rotation and the cache write in its epilogue, where `linear`
+    would take the persistent pairs kernel anyway: head sizes 64, 128 and 256, the whole head rotated."""
+    from . import linear as linear_module
+    nq, nkv, d = part.num_heads, part.num_kv_heads, part.head_dim
+    N, K = ctx.n_tokens, part.hidden_size
+    if d not in ops.PAIR_QKV_HEAD_DIMS or K % 8 != 0 or N < fused_projection_rows:
+        return False
+    if cos is not None and 2 * cos.shape[-1] != d:
+        return False
+    if linear_module.set_bf16_kernel_active() or linear_module.tcgen05_form(N, (nq + 2 * nkv) * d, K) != "pair" \
+            or linear_module.pair_plan(N, (nq + 2 * nkv) * d, K)[1] != 1:
+        return False
+    ops.gemm_tcgen05_pair_qkv(x, part.w_qkv, q, cache.keys, cache.values, q_norm_w, k_norm_w, cos, sin, eps, ctx.token_seq,
+                              ctx.token_pos, table, N, nq, nkv, d, write_kv=not cache.shared)
+    return True
+
+
 _sm_counts = {}
 
 
@@ -179,9 +206,14 @@ def _prefill_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
 
 
 tc_prefill_rows = 128     # from this many new tokens of the longest sequence on, the tcgen05 kernel runs
+# From this many tokens in a step on, the q/k/v product does norm, rotation and cache write in its epilogue: with
+# several tiles per pair of SMs the longer epilogue hides under the next tile's K steps (measured: 8,192 tokens
+# 321-338 us against 381-412 for product + qkv_prepare, 2,048 tokens 83.5 against 86, 512 tokens 41 against 34).
+fused_projection_rows = 2048
 
 DECODE_KERNELS.append(_decode_split_kernel)
 FUSED_DECODE_KERNELS.append(_decode_fused_kernel)
+FUSED_PROJECTION_KERNELS.append(_projection_pair_kernel)
 PREFILL_KERNELS.append(_prefill_tcgen05_kernel)
 PREFILL_KERNELS.append(_prefill_flash_kernel)
 

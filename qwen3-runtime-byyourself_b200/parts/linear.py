@@ -28,6 +28,11 @@ def set_bf16_kernel(fn: Optional[Callable]) -> None:
     _bf16_kernel = fn
 
 
+def set_bf16_kernel_active() -> bool:
+    """Whether another kernel has been registered for bfloat16 products (fused projections then stand back)."""
+    return _bf16_kernel is not None
+
+
 # Microseconds per 64-wide K step of a tile and per block for its start and end, measured on B200.
 _STEP_US = {"pair": 0.33, "prompt128": 0.29, "weights_first": 0.40}
 _BLOCK_US = {"pair": 8.0, "prompt128": 5.0}

@@ -751,6 +751,71 @@ def test_tcgen05_pair_product_with_k_split_over_a_cluster(M, N, K, splits, out_d
         ops.gemm_tcgen05_pair(x, w, out, splits=5)
 
 
+@pytest.mark.parametrize("nq,nkv,d,K", [(4, 2, 128, 256), (3, 1, 64, 136), (2, 2, 256, 64), (8, 2, 128, 512)])
+@pytest.mark.parametrize("with_norm,with_tables", [(True, True), (False, True), (True, False)])
+def test_tcgen05_pair_product_with_the_qkv_epilogue(nq, nkv, d, K, with_norm, with_tables):
+    """The q/k/v product with norm, rotation and cache write in its epilogue, for prompts of unequal lengths that
+    continue sequences already in the cache (positions do not start at 0) over shuffled pages: q and the written
+    keys and values agree with the plain float64 norm and rotation of the bfloat16-rounded product, and with the
+    product + qkv_prepare pair of kernels to within one rounding; cache rows of other tokens are not touched; a layer
+    that reads another layer's cache writes nothing."""
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(nq + d + K)
+    eps, theta = 1e-5, 30000.0
+    before, new = [0, 70, 5], [150, 9, 300]                   # tokens already cached, tokens of this step
+    totals = [a + b for a, b in zip(before, new)]
+    table, kp, vp = paged_case(rng, totals, nkv, d, "bfloat16")
+    kp.fill_(7.0); vp.fill_(7.0)                              # a canary in every cell
+    table_d = torch.as_tensor(table).cuda()
+    seq = np.concatenate([np.full(n, s) for s, n in enumerate(new)]).astype(np.int32)
+    pos = np.concatenate([np.arange(a, a + n) for a, n in zip(before, new)]).astype(np.int32)
+    M = len(seq)
+    seq_d, pos_d = torch.as_tensor(seq).cuda(), torch.as_tensor(pos).cuda()
+    x = dev(rng.normal(0, 1, (M, K)), "bfloat16")
+    w = dev(rng.normal(0, 1.0 / math.sqrt(K), ((nq + 2 * nkv) * d, K)), "bfloat16")
+    qw = dev(1 + rng.normal(0, 0.1, d), "float32") if with_norm else None
+    kw = dev(1 + rng.normal(0, 0.1, d), "float32") if with_norm else None
+    cos, sin = plain.rope_table(max(totals), d, theta)
+    cos_d, sin_d = (dev(cos, "float32"), dev(sin, "float32")) if with_tables else (None, None)
+    q = torch.full((M, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tcgen05_pair_qkv(x, w, q, kp, vp, qw, kw, cos_d, sin_d, eps, seq_d, pos_d, table_d, M, nq, nkv, d)
+    assert ops.tcgen05_status("cuda") == 0
+    # the two-kernel path on a cache of its own
+    kp2, vp2 = torch.full_like(kp, 7.0), torch.full_like(vp, 7.0)
+    qkv = torch.empty(M, (nq + 2 * nkv) * d, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tcgen05_pair(x, w, qkv)
+    q2 = torch.empty_like(q)
+    ops.qkv_prepare(qkv, q2, kp2, vp2, qw, kw, cos_d, sin_d, seq_d, pos_d, table_d, M, nq, nkv, d, eps)
+    # plain: norm and rotation of the rounded product
+    raw = back(qkv).reshape(M, nq + 2 * nkv, d)
+    rnd = plain.round_bf16
+    qs, ks, vs = raw[:, :nq], raw[:, nq:nq + nkv], raw[:, nq + nkv:]
+    if with_norm:
+        qs, ks = plain.rms_norm(qs, back(qw), eps, rnd), plain.rms_norm(ks, back(kw), eps, rnd)
+    if with_tables:
+        qs, ks = plain.apply_rope(qs, pos, cos, sin, rnd), plain.apply_rope(ks, pos, cos, sin, rnd)
+    scale = max(1.0, float(np.abs(qs).max()), float(np.abs(ks).max()))
+    assert np.max(np.abs(back(q).reshape(M, nq, d) - qs)) <= 2.0 ** -7 * scale
+    assert np.max(np.abs(back(q) - back(q2))) <= 2.0 ** -7 * scale
+    written = torch.zeros(kp.shape[0], 64, dtype=torch.bool)
+    for t in range(M):
+        page, row = int(table[seq[t], pos[t] // 64]), int(pos[t] % 64)
+        written[page, row] = True
+        assert np.max(np.abs(back(kp[page, :, row]) - ks[t])) <= 2.0 ** -7 * scale, t
+        assert np.array_equal(back(vp[page, :, row]), vs[t]), t
+    touched = ((kp != 7.0) | (vp != 7.0)).any(dim=-1).any(dim=1).cpu()
+    assert torch.equal(touched, written)
+    assert np.max(np.abs(back(kp) - back(kp2))) <= 2.0 ** -7 * scale and torch.equal(vp, vp2)
+    # a layer that reads another layer's cache
+    kp3, vp3 = torch.full_like(kp, 7.0), torch.full_like(vp, 7.0)
+    q3 = torch.empty_like(q)
+    ops.gemm_tcgen05_pair_qkv(x, w, q3, kp3, vp3, qw, kw, cos_d, sin_d, eps, seq_d, pos_d, table_d, M, nq, nkv, d, write_kv=False)
+    assert torch.equal(q3, q) and bool((kp3 == 7.0).all()) and bool((vp3 == 7.0).all())
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tcgen05_pair_qkv(x, w[:, :K - 8].contiguous(), q3, kp3, vp3, qw, kw, cos_d, sin_d, eps, seq_d, pos_d, table_d,
+                                  M, nq, nkv, d)
+
+
 @pytest.mark.parametrize("M,inter,K,splits", [(300, 160, 192, 2), (512, 1536, 512, 3), (77, 112, 320, 4)])
 def test_tcgen05_pair_gated_epilogue_with_k_split(M, inter, K, splits):
     """SiLU and gating after the partial tiles have met: equal to the split product + silu_mul, bit for bit."""
