@@ -49,7 +49,8 @@ constexpr int SMEM_BYTES = SMEM_PIPE > SMEM_MERGE ? SMEM_PIPE : SMEM_MERGE;
 constexpr int SMEM_PREP = (16 + 2) * D * 2;
 constexpr int SMEM_RESULT = 16 * (D + 2) * 4;
 constexpr int SMEM_FUSED = SMEM_BYTES + (SMEM_PREP > SMEM_RESULT ? SMEM_PREP : SMEM_RESULT);
-constexpr int MAX_CLUSTER = 8;                     // the portable cluster size: the fused form takes up to 8 splits
+constexpr int MAX_CLUSTER = 16;                    // the fused form takes up to 16 splits (above 8 the cluster size is the
+                                                   // device's non-portable one, asked for at the launch)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -501,7 +502,7 @@ Q3_EXPORT int q3_attention_decode_bf16(const void* q, const void* k_pages, const
 
 // The whole attention of a decode step in one launch (see the top of the file): `qkv` is the projection output
 // [tokens, (nq + 2 nkv) * head size]; norm weights and rotation tables ([positions, rotary_dim / 2]) may be null;
-// `rotary_dim` 0 = the head size; `n_splits` <= 8.
+// `rotary_dim` 0 = the head size; `n_splits` <= 16.
 Q3_EXPORT int q3_attention_decode_fused_bf16(const void* qkv, void* k_pages, void* v_pages, void* out, const float* q_norm_w,
                                              const float* k_norm_w, const float* cos_tab, const float* sin_tab, float eps,
                                              const int* token_seq, const int* token_pos, const int* page_table,
@@ -515,9 +516,19 @@ Q3_EXPORT int q3_attention_decode_fused_bf16(const void* qkv, void* k_pages, voi
     if (n_tokens > 65535 || nkv > 65535) return Q3_ERR_TOO_LARGE;
     if (!aligned16(qkv) || !aligned16(k_pages) || !aligned16(v_pages)) return Q3_ERR_MISALIGNED;
     cudaStream_t stream = (cudaStream_t)stream_;
-    static Q3PerDevice configured;
+    static Q3PerDevice configured, configured_large;
     cudaError_t e = q3_allow_shared_memory(decode_split_kernel<true>, SMEM_FUSED, configured);
     if (e != cudaSuccess) return (int)e;
+    if (n_splits > 8) {                                     // one sequence, or two, with a long context: clusters of up to 16
+        int device = 0;
+        if ((e = cudaGetDevice(&device)) != cudaSuccess) return (int)e;
+        if (device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
+        if (!configured_large.done[device]) {
+            e = cudaFuncSetAttribute(decode_split_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            if (e != cudaSuccess) return (int)e;
+            configured_large.done[device] = true;
+        }
+    }
     FusedArgs fused;
     fused.qkv = (const bf16*)qkv;
     fused.out = (bf16*)out;

@@ -402,7 +402,7 @@ def attention_decode(q, k_pages, v_pages, out, scratch, token_seq, token_pos, pa
     return out
 
 
-FUSED_DECODE_MAX_SPLITS = 8
+FUSED_DECODE_MAX_SPLITS = 16
 
 
 def attention_decode_fused(qkv, k_pages, v_pages, out, q_norm_w, k_norm_w, cos, sin, eps: float, token_seq, token_pos,

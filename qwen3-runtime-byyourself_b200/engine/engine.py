@@ -125,6 +125,9 @@ def build_context(cache, meta: "_MetaBuffer", scratch, dtype, max_positions, slo
                          want_all=(R == N and list(want_rows) == list(range(N))))
 
 
+FEW_ROWS, LONG_CONTEXT = 2, 4096     # see Engine._step_captured
+
+
 def decode_bucket(n: int) -> int:
     """Fixed batch sizes for captured decode steps: 1..8 exactly, then multiples of 8, of 32 above 64."""
     if n <= 8:
@@ -140,15 +143,16 @@ class _DecodeGraph:
     Rows beyond the live sequences are padding: token 0 at position 0 of the spare page that
     belongs to no sequence; their logits are computed and dropped, no live row reads them."""
 
-    def __init__(self, engine: "Engine", rows: int):
+    def __init__(self, engine: "Engine", rows: int, max_context: Optional[int] = None):
         self.engine, self.rows = weakref.proxy(engine), rows      # no cycle: an engine dies with its last reference
+        max_context = max_context or engine.max_seq_len           # the bound on a sequence's length the parts may count on
         cache = engine.cache
         self.layout = _MetaLayout(cache, rows, rows, rows)
         self.meta = _MetaBuffer(engine.device)
         self.meta.reserve(self.layout.total)
         self.scratch = Scratch(engine.device, guard=engine.scratch.guard)
         self.ctx = context_views(cache, self.meta.dev, self.layout, rows, rows, rows, self.scratch, engine.dtype,
-                                 engine.max_seq_len, is_decode=True, max_new=1, max_context=engine.max_seq_len,
+                                 engine.max_seq_len, is_decode=True, max_new=1, max_context=max_context,
                                  want_all=True)
         self.graph = None
         self.logits = None
@@ -220,6 +224,7 @@ class Engine:
         # a mixer whose step depends on host values (not only on the context's device fields) opts out
         self.use_graphs = use_graphs and all(getattr(b.mixer, "graph_safe", True) for b in model.blocks)
         self._graphs = {}
+        self._long_graphs = {}     # captured steps of up to FEW_ROWS sequences whose contexts exceed LONG_CONTEXT
         self.device_tokens = True  # `step` can read a decode step's token ids on the device
         self.launches = 0          # kernels of this library launched by steps (replayed graph nodes included)
         self.last_upload_bytes = 0
@@ -228,7 +233,7 @@ class Engine:
         """Activation buffers (of the launched steps and of every captured decode step) that a kernel wrote beyond;
         empty unless the engine was built with `guard_scratch` and something is wrong."""
         bad = list(self.scratch.violations())
-        for graph in self._graphs.values():
+        for graph in list(self._graphs.values()) + list(self._long_graphs.values()):
             bad += graph.scratch.violations()
         return bad
 
@@ -333,9 +338,14 @@ class Engine:
 
     def _step_captured(self, slots, pos0, token_ids, want_rows, device_tokens):
         rows = decode_bucket(len(slots))
-        graph = self._graphs.get(rows)
+        # a few sequences with long contexts are a workload of their own (one sequence's keys have to fill the GPU):
+        # such steps are captured apart, with `ctx.max_context` beyond LONG_CONTEXT, and parts may choose by it
+        few_and_long = rows <= FEW_ROWS and self.max_seq_len > LONG_CONTEXT and max(pos0) + 1 > LONG_CONTEXT
+        graphs = self._long_graphs if few_and_long else self._graphs
+        graph = graphs.get(rows)
         if graph is None:
-            graph = self._graphs[rows] = _DecodeGraph(self, rows)
+            bound = self.max_seq_len if few_and_long or rows > FEW_ROWS else min(self.max_seq_len, LONG_CONTEXT)
+            graph = graphs[rows] = _DecodeGraph(self, rows, bound)
         logits = graph.run(slots, pos0, token_ids, device_tokens)
         self.last_upload_bytes = graph.meta.bytes_last_upload
         if not want_rows:

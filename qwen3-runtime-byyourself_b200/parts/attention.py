@@ -147,11 +147,17 @@ def _decode_split_kernel(part, q, cache, out, ctx, table) -> bool:
 
 def _decode_fused_kernel(part, qkv, cache, out, ctx, table, q_norm_w, k_norm_w, eps, cos, sin) -> bool:
     """Norm, rotation, cache write, split-key attention and the merge of the splits (inside a thread-block
-    cluster) in one launch: bfloat16, groups of up to 16 query heads, up to 8 splits."""
+    cluster) in one launch: bfloat16, groups of up to 16 query heads, up to 16 splits."""
     nq, nkv, d = part.num_heads, part.num_kv_heads, part.head_dim
     if nq // nkv > 16:
         return False
-    splits = min(ops.attention_decode_splits(ctx.n_tokens, nkv, _sm_count(ctx.device)), ops.FUSED_DECODE_MAX_SPLITS)
+    splits = ops.attention_decode_splits(ctx.n_tokens, nkv, _sm_count(ctx.device))
+    if splits > 8:
+        # more than eight blocks per (sequence, kv head) - a cluster beyond the portable size - pay for one or two
+        # sequences with long contexts only (one sequence of 32,768 keys: 39.6 us with 16 splits against 53.8 with 8;
+        # two: 54.7 with 12 against 64.8; at 2,048 keys 11.8 against 11.1)
+        wide = min(splits, max(8, wide_cluster_blocks // (ctx.n_tokens * nkv)), ops.FUSED_DECODE_MAX_SPLITS)
+        splits = wide if ctx.max_context > long_context_keys else 8
     ops.attention_decode_fused(qkv, cache.keys, cache.values, out, q_norm_w, k_norm_w, cos, sin, eps, ctx.token_seq,
                                ctx.token_pos, table, ctx.n_tokens, nq, nkv, d, part.scale, part.window, splits,
                                write_kv=not cache.shared)
@@ -205,6 +211,8 @@ def _prefill_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
     return True
 
 
+long_context_keys = 4096  # a decode step whose sequences may be longer takes wider clusters (if they are few)
+wide_cluster_blocks = 200 # blocks of a decode step with clusters beyond the portable size
 tc_prefill_rows = 128     # from this many new tokens of the longest sequence on, the tcgen05 kernel runs
 # From this many tokens in a step on, the q/k/v product does norm, rotation and cache write in its epilogue: with
 # several tiles per pair of SMs the longer epilogue hides under the next tile's K steps (measured: 8,192 tokens

@@ -439,7 +439,7 @@ def test_decode_attention_fused_kernel(nq, nkv, d):
     before_k, before_v = kp.clone(), vp.clone()
     args = (dev(qw, "float32"), dev(kw, "float32"), dev(cos, "float32"), dev(sin, "float32"), eps, seq, pos, table_d, B, nq, nkv, d,
             d ** -0.5, None)
-    for splits in (1, 2, 5, 8):
+    for splits in (1, 2, 5, 8, 11, 16):
         kp.copy_(before_k); vp.copy_(before_v)
         out = torch.zeros(B, nq * d, dtype=torch.bfloat16, device="cuda")
         ops.attention_decode_fused(qkv_d, kp, vp, out, *args, splits)
@@ -461,7 +461,7 @@ def test_decode_attention_fused_kernel(nq, nkv, d):
     assert torch.equal(kp, snapshot_k) and torch.equal(vp, snapshot_v)
     assert np.max(np.abs(back(out2) - want)) <= 2.5e-2
     with pytest.raises(ops.KernelError):
-        ops.attention_decode_fused(qkv_d, kp, vp, out2, *args, 9)
+        ops.attention_decode_fused(qkv_d, kp, vp, out2, *args, 17)
 
 
 @pytest.mark.parametrize("nq,nkv,d,rot", [(4, 2, 64, 32), (8, 1, 128, 64), (6, 3, 48, 16), (5, 5, 80, 2), (2, 2, 256, 254),

@@ -248,3 +248,37 @@ def test_8b_widths_in_unequal_batches(wide, dtype, monkeypatch):
         assert calls["attention_tc"] == 2 * 2 and calls["decode_attention"] > 0 and calls["skinny"] > 0, calls
     del engine, model
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_few_sequences_growing_past_the_long_context_bound(folders, name, dtype, monkeypatch):
+    """One sequence, then two of unequal lengths, decoded token by token from below the bound at which the engine
+    captures steps of a few sequences apart (lowered to 200 tokens here) to beyond it: the logits agree with the
+    plain model on both sides of the bound and at the step that crosses it, both sets of captured steps were used,
+    and in bfloat16 the one-launch attention ran with clusters beyond the portable size (more than eight key
+    splits per sequence and kv head, some of them without a page)."""
+    from qwen3_b200.csrc import ops
+    from qwen3_b200.engine import engine as engine_module
+    from qwen3_b200.parts import attention as attention_part
+    monkeypatch.setattr(engine_module, "LONG_CONTEXT", 200)
+    monkeypatch.setattr(attention_part, "long_context_keys", 200)
+    splits_seen = set()
+    real = ops.attention_decode_fused
+
+    def fused(*a, **k):
+        splits_seen.add(a[18] if len(a) > 18 else k.get("n_splits"))
+        return real(*a, **k)
+    monkeypatch.setattr(ops, "attention_decode_fused", fused)
+    folder, weights = folders[name]
+    cfg = tiny(name)
+    for lengths, prompts in (([230], {"r0": 180}), ([215, 240], {"r0": 190, "r1": 170})):
+        requests = make_requests(cfg, lengths, seed=len(lengths))
+        steps, rows = schedules.batched(requests, prompts, len(lengths))
+        engine = engine_for(folder, dtype, schedules.peak_tokens(steps))
+        got = run_steps(engine, steps, rows)
+        check(got, requests, cfg, weights, dtype, f"{len(lengths)} sequences across the bound")
+        assert engine._graphs and engine._long_graphs, (list(engine._graphs), list(engine._long_graphs))
+        engine.check_kernels()
+    if dtype == "bfloat16":
+        assert max(splits_seen) > 8 and 8 in splits_seen, splits_seen
