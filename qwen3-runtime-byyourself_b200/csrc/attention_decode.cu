@@ -203,7 +203,6 @@ decode_split_kernel(const bf16* __restrict__ q, const bf16* k_pages, const bf16*
                     const int* __restrict__ token_pos, const int* __restrict__ page_table, int pages_per_seq, int nq,
                     int nkv, float scale_log2, int window, const FusedArgs fused) {
     extern __shared__ __align__(16) unsigned char smem[];
-    pdl_wait();
     const int split = blockIdx.x, n_splits = gridDim.x, kvh = blockIdx.y, t = blockIdx.z;
     const int G = nq / nkv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -230,6 +229,9 @@ decode_split_kernel(const bf16* __restrict__ q, const bf16* k_pages, const bf16*
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) issue(s);
+    // the pages and the step's positions do not depend on the kernel before this one (the new token's key and
+    // value are this kernel's own to write); its output - the projections - is read from here on
+    pdl_wait();
 
     // the block that holds the sequence's last page owns the new token's key and value
     const bool owner = FUSED && fused.write_kv && count > 0 && pg_end == first_page + n_pages;

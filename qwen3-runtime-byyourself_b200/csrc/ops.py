@@ -31,8 +31,9 @@ class KernelError(RuntimeError):
 # weights) while the kernel before it on the stream drains, and waits for that kernel's results only where it
 # first needs them.  By default the sources named here launch their kernels that way: measured on whole decode
 # steps of an 8B-sized model, the TMA + tcgen05 products gain 2.5-5 % at batches of 16 to 64 (4.92 -> 4.74 ms a
-# step at batch 16), while the few-row product and the small kernels around it lose (batch 8: chains of waiting
-# blocks take the room that a kernel's own later waves need).  QWEN3_B200_PDL=1 / =0 turns it on / off for all.
+# step at batch 16), while the few-row product loses (batch 8: chains of waiting blocks take the room that a kernel's
+# own later waves need) and the decode attention, which asks for its first pages before it waits, gains 0.5 % at batch
+# 16 and 32 and loses 0.3 % at batch 64.  QWEN3_B200_PDL=1 / =0 turns it on / off for all.
 PDL_SOURCES = ("gemm_tcgen05.cu",)
 _pdl_override = {"1": True, "0": False}.get(os.environ.get("QWEN3_B200_PDL", ""))
 _libs = {}
