@@ -502,6 +502,37 @@ Q3_EXPORT int q3_attention_decode_bf16(const void* q, const void* k_pages, const
                           (const float*)part_o, (const float*)part_ml, (bf16*)out, nq, n_splits);
 }
 
+// The most key splits (blocks of a cluster) the one-launch form can take on the current device: 16 where a cluster of
+// that size can be placed (it is beyond the portable size), else 8.
+Q3_EXPORT int q3_attention_decode_fused_max_splits() {
+    static int cached[64];
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 8;
+    if (cached[device] == 0) {
+        cached[device] = 8;
+        static Q3PerDevice configured;
+        if (q3_allow_shared_memory(decode_split_kernel<true>, SMEM_FUSED, configured) == cudaSuccess &&
+            cudaFuncSetAttribute(decode_split_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(MAX_CLUSTER, 8, 1);
+            cfg.blockDim = dim3(WARPS * 32);
+            cfg.dynamicSmemBytes = SMEM_FUSED;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = MAX_CLUSTER;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, decode_split_kernel<true>, &cfg) == cudaSuccess && clusters > 0)
+                cached[device] = MAX_CLUSTER;
+        }
+        cudaGetLastError();        // a refusal above is an answer, not an error to keep
+    }
+    return cached[device];
+}
+
 // The whole attention of a decode step in one launch (see the top of the file): `qkv` is the projection output
 // [tokens, (nq + 2 nkv) * head size]; norm weights and rotation tables ([positions, rotary_dim / 2]) may be null;
 // `rotary_dim` 0 = the head size; `n_splits` <= 16.

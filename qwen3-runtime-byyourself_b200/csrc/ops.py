@@ -404,6 +404,19 @@ def attention_decode(q, k_pages, v_pages, out, scratch, token_seq, token_pos, pa
 
 
 FUSED_DECODE_MAX_SPLITS = 16
+_fused_max_splits = {}
+
+
+def attention_decode_fused_max_splits(d: int, device) -> int:
+    """The most key splits `attention_decode_fused` takes on `device` for head size `d`: 16 where the device places
+    clusters of 16 blocks (beyond the portable size), else 8."""
+    key = (d, torch.device(device))
+    got = _fused_max_splits.get(key)
+    if got is None:
+        fn = _fn_untimed("attention_decode.cu", "q3_attention_decode_fused_max_splits", [], defines=(f"Q3_HEAD_DIM={d}",))
+        with torch.cuda.device(key[1]):
+            got = _fused_max_splits[key] = int(fn())
+    return got
 
 
 def attention_decode_fused(qkv, k_pages, v_pages, out, q_norm_w, k_norm_w, cos, sin, eps: float, token_seq, token_pos,

@@ -77,6 +77,7 @@ int q3_attention_decode_bf16(const void* q, const void* k_pages, const void* v_p
                              float scale, int window, int n_splits, void* stream);
 /* the whole attention of a decode step from the q/k/v projection's output: norm, rotation, cache write, attention,
    merge of up to 8 splits inside a thread-block cluster; no scratch */
+int q3_attention_decode_fused_max_splits(void);   /* 16 where clusters of 16 blocks can be placed, else 8 */
 int q3_attention_decode_fused_bf16(const void* qkv, void* k_pages, void* v_pages, void* out, const float* q_norm_w,
                                    const float* k_norm_w, const float* cos_tab, const float* sin_tab, float eps, const int* token_seq,
                                    const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv,

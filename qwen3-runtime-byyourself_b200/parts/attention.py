@@ -156,7 +156,7 @@ def _decode_fused_kernel(part, qkv, cache, out, ctx, table, q_norm_w, k_norm_w, 
         # more than eight blocks per (sequence, kv head) - a cluster beyond the portable size - pay for one or two
         # sequences with long contexts only (one sequence of 32,768 keys: 39.6 us with 16 splits against 53.8 with 8;
         # two: 54.7 with 12 against 64.8; at 2,048 keys 11.8 against 11.1)
-        wide = min(splits, max(8, wide_cluster_blocks // (ctx.n_tokens * nkv)), ops.FUSED_DECODE_MAX_SPLITS)
+        wide = min(splits, max(8, wide_cluster_blocks // (ctx.n_tokens * nkv)), ops.attention_decode_fused_max_splits(d, ctx.device))
         splits = wide if ctx.max_context > long_context_keys else 8
     ops.attention_decode_fused(qkv, cache.keys, cache.values, out, q_norm_w, k_norm_w, cos, sin, eps, ctx.token_seq,
                                ctx.token_pos, table, ctx.n_tokens, nq, nkv, d, part.scale, part.window, splits,
