@@ -202,3 +202,34 @@ def test_running_ahead_gives_the_same_tokens_and_frees_everything():
     assert chooser.calls[0] == ([0, 1, 2, 3, 4], [0] * 5) and chooser.calls[1][1][0] == 1
     again = q.generate(AheadEngine(max_tokens=64 * 2), prompts, AheadArgmax(), max_new_tokens=9, stop_token_ids=stops)
     assert [r.token_ids for r in again] == [r.token_ids for r in want]       # several batches, slots reused
+
+
+def test_random_workloads_against_the_scripted_rule():
+    """Hundreds of random workloads (prompt lengths, budgets, stop sets, cache sizes, slot counts, batch sizes)
+    through the loop with the scripted engine: every request gets exactly the tokens and the stop reason the
+    rule gives, whatever batches the planner made, and the cache is empty afterwards."""
+    rng = np.random.default_rng(123)
+    for trial in range(150):
+        vocab = int(rng.integers(5, 60))
+        n_slots = int(rng.integers(1, 7))
+        pages = int(rng.integers(2, 9))
+        engine = ScriptedEngine(vocab=vocab, max_tokens=64 * pages, max_seq_len=128, n_slots=n_slots)
+        max_new = int(rng.integers(0, 40))
+        n = int(rng.integers(0, 12))
+        prompts = [[int(t) for t in rng.integers(0, vocab, int(rng.integers(1, 128 - max_new + 1)))] for _ in range(n)]
+        stops = [int(s) for s in rng.choice(vocab, size=int(rng.integers(0, 4)), replace=False)]
+        batch_size = None if rng.integers(0, 2) else int(rng.integers(1, 5))
+        results = q.generate(engine, prompts, Argmax(), max_new_tokens=max_new, stop_token_ids=stops, batch_size=batch_size)
+        assert len(results) == n
+        for prompt, r in zip(prompts, results):
+            want, why = expected(prompt, max_new, set(stops), vocab)
+            assert (r.token_ids, r.stop_reason) == (want, why), (trial, prompt, max_new, stops)
+        assert engine.cache.pages_held() == 0 and not engine.sums
+        assert engine.peak_slots <= min(n_slots, batch_size or n_slots)
+        # the planner alone: batches are consecutive, respect slots, pages and the batch size, and cover every request
+        if n:
+            batches = q.plan_batches([len(p) for p in prompts], max_new, pages, n_slots, 64, batch_size)
+            assert [i for b in batches for i in b] == list(range(n))
+            for b in batches:
+                assert len(b) <= min(n_slots, batch_size or n_slots)
+                assert sum(-(-(len(prompts[i]) + max_new) // 64) for i in b) <= pages
