@@ -221,6 +221,11 @@ def test_random_workloads_against_the_scripted_rule():
         batch_size = None if rng.integers(0, 2) else int(rng.integers(1, 5))
         results = q.generate(engine, prompts, Argmax(), max_new_tokens=max_new, stop_token_ids=stops, batch_size=batch_size)
         assert len(results) == n
+        # the loop that keeps the device one step ahead of the host decides the same
+        ahead = AheadEngine(vocab=vocab, max_tokens=64 * pages, max_seq_len=128, n_slots=n_slots)
+        ran_ahead = q.generate(ahead, prompts, AheadArgmax(), max_new_tokens=max_new, stop_token_ids=stops, batch_size=batch_size)
+        assert [(r.token_ids, r.stop_reason) for r in ran_ahead] == [(r.token_ids, r.stop_reason) for r in results], trial
+        assert ahead.cache.pages_held() == 0 and not ahead.sums
         for prompt, r in zip(prompts, results):
             want, why = expected(prompt, max_new, set(stops), vocab)
             assert (r.token_ids, r.stop_reason) == (want, why), (trial, prompt, max_new, stops)
