@@ -78,6 +78,33 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Two floats in one 64-bit register, and the arithmetic of this architecture that takes both at once.
+__device__ __forceinline__ uint64_t pack_f32x2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -245,9 +272,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             // the page's maximum on the raw dots (the scale is positive), four chains side by side
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 64; c += 4) {
+            for (int c = 0; c < 64; c += 8) {                               // two scores per instruction and chain
 #pragma unroll
-                for (int e = 0; e < 4; ++e) mx[e] = fmaxf(mx[e], __uint_as_float(s[c + e]));
+                for (int e = 0; e < 4; ++e) mx[e] = max3(mx[e], __uint_as_float(s[c + e]), __uint_as_float(s[c + 4 + e]));
             }
             const float m_page = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
             float alpha = 1.0f;
@@ -261,18 +288,24 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
             // p = 2^(dot * scale - m): one multiply-add and one ex2 per score, four sums side by side
             const float neg_m = -m_run;
-            float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // (the multiply-adds and the sums take two scores an instruction: fma.rn.f32x2, add.f32x2)
+            const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(neg_m, neg_m);
+            uint64_t part2[2] = {pack_f32x2(0.0f, 0.0f), pack_f32x2(0.0f, 0.0f)};
             uint32_t p[32];
 #pragma unroll
             for (int c = 0; c < 64; c += 4) {
-                const float a = ex2_approx(fmaf(__uint_as_float(s[c]), scale_log2, neg_m));
-                const float b = ex2_approx(fmaf(__uint_as_float(s[c + 1]), scale_log2, neg_m));
-                const float e = ex2_approx(fmaf(__uint_as_float(s[c + 2]), scale_log2, neg_m));
-                const float f = ex2_approx(fmaf(__uint_as_float(s[c + 3]), scale_log2, neg_m));
-                part[0] += a; part[1] += b; part[2] += e; part[3] += f;
+                float x0, x1, x2, x3;
+                unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), scale2, neg_m2), x0, x1);
+                unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])), scale2, neg_m2), x2, x3);
+                const float a = ex2_approx(x0), b = ex2_approx(x1), e = ex2_approx(x2), f = ex2_approx(x3);
+                part2[0] = add_f32x2(part2[0], pack_f32x2(a, b));
+                part2[1] = add_f32x2(part2[1], pack_f32x2(e, f));
                 p[c >> 1] = pack_bf16(a, b);
                 p[(c >> 1) + 1] = pack_bf16(e, f);
             }
+            float part[4];
+            unpack_f32x2(part2[0], part[0], part[1]);
+            unpack_f32x2(part2[1], part[2], part[3]);
             const float sum = (part[0] + part[1]) + (part[2] + part[3]);
             l_run = l_run * alpha + sum;
             if (j > 0) {
@@ -285,8 +318,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                         uint32_t o[32];
                         tc_ld32(t_row + COL_O + c, o);
                         tc_wait_ld();
+                        const uint64_t alpha2 = pack_f32x2(alpha, alpha);
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                        for (int e = 0; e < 32; e += 2) {
+                            float x, y;
+                            unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(o[e]), __uint_as_float(o[e + 1])), alpha2), x, y);
+                            o[e] = __float_as_uint(x);
+                            o[e + 1] = __float_as_uint(y);
+                        }
                         tc_st32(t_row + COL_O + c, o);
                     }
                 }
