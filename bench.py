@@ -414,6 +414,11 @@ def main() -> int:
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
             moved = weight_bytes_per_step(cfg, layers, b) + r["cached_tokens"] * engine.cache.bytes_per_token()
             points[f"decode_b{b}_hbm_frac"] = round(moved / (r["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+        # a batch between the two, at the headline's context: the TMA + tcgen05 product instead of the few-row one
+        r = decode_run(q, engine, sampler, torch, rng, 16, CONTEXT - warmup - min(args.steps, 32) - 1, min(args.steps, 32), warmup, clocks)
+        points[f"decode_b16_context{CONTEXT}"] = round(r["tok_s"], 1)
+        moved = weight_bytes_per_step(cfg, layers, 16) + r["cached_tokens"] * engine.cache.bytes_per_token()
+        points[f"decode_b16_context{CONTEXT}_hbm_frac"] = round(moved / (r["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
         for factor in (2, 4):
             ctx = factor * CONTEXT
             r = decode_run(q, engine, sampler, torch, rng, batch, ctx - warmup - min(args.steps, 32) - 1, min(args.steps, 32), warmup,
